@@ -6,7 +6,12 @@ SRC := $(wildcard llark_b200/csrc/*.cu)
 OBJ := $(patsubst llark_b200/csrc/%.cu,build/%.o,$(SRC))
 LIB := llark_b200/libllark_b200.so
 
+# the subset a native checkpoint of a layer-list decoder needs: GEMM core, decode linears, generation-path ops
+SERVE_OBJ := build/gemm_tcgen05.o build/gemv.o build/seq_ops.o build/seq_mixers.o
+LIB_SERVE := llark_b200/libllark_serve.so
+
 all: $(LIB)
+serve: $(LIB_SERVE)
 
 build/%.o: llark_b200/csrc/%.cu llark_b200/csrc/common.cuh include/llark_b200.h
 	@mkdir -p build
@@ -18,6 +23,9 @@ build/attention_tc_alibi.o: llark_b200/csrc/attention_tc.cu
 $(LIB): $(OBJ)
 	$(NVCC) $(ARCH) -shared -o $@ $(OBJ) -lnccl
 
+$(LIB_SERVE): $(SERVE_OBJ)
+	$(NVCC) $(ARCH) -shared -o $@ $(SERVE_OBJ)
+
 clean:
-	rm -rf build $(LIB)
-.PHONY: all clean
+	rm -rf build $(LIB) $(LIB_SERVE)
+.PHONY: all serve clean

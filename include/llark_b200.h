@@ -265,6 +265,64 @@ int llark_v32_attn_fwd(const float* qkv, const unsigned char* key_mask, float* o
 int llark_v32_ce_fwd(const float* logits, long long ldv, int V, const long long* labels, int B, int S, float* row_loss,
                      float* loss_out, cudaStream_t stream);
 
+/* ---- generation path of layer-list decoders (csrc/seq_ops.cu, csrc/seq_mixers.cu). The reference generates through
+ * transformers' GenerationMixin with a per-layer key / value cache (m2t/infer.py:146-152 -> m2t/models/llamav2.py:339-365);
+ * these are the per-step ops of decoders assembled from other parts (sliding-window attention, gated linear recurrence,
+ * short convolutions, norm-on-output residual blocks), which the reference does not have. One step is a PACKED batch:
+ * the new tokens of all requests concatenated [n_tok, width]; tok_seq[t] = request of token t, cu[b] = first row of
+ * request b (cu[n_seq] = n_tok), pos0[b] = position of that row in its sequence, slot[b] = the request's row in every
+ * state store. The residual stream, norms, scores, softmax and recurrent state are fp32; `act_fp32` selects the
+ * activation / matrix dtype (0: bf16, 1: float = the all-fp32 mode). */
+int llark_seq_embed(const int* ids, const int* tok_seq, const int* cu, const int* pos0, const void* table,
+                    const void* pos_table, float scale, float* x, int n_tok, int C, int act_fp32, cudaStream_t stream);
+/* y = h + conv(h): causal depthwise convolution over time, w fp32 [C, taps], tail fp32 [slots, taps-1, C] = the last
+ * taps-1 inputs of each request, oldest first. inline_tail = 1 (every request brings one token) also shifts the tail;
+ * otherwise call llark_seq_conv_tail after it. */
+int llark_seq_short_conv(const float* h, const float* w, float* tail, const int* tok_seq, const int* cu, const int* slot,
+                         void* y, int n_tok, int C, int taps, int inline_tail, int act_fp32, cudaStream_t stream);
+int llark_seq_conv_tail(const float* h, float* tail, const int* cu, const int* slot, int n_seq, int C, int taps,
+                        cudaStream_t stream);
+/* x_out = x + y / sqrt(mean(y^2) + eps) * w (row-wise; x_out may not alias x when other rows of x are still read by the
+ * caller); x_act (optional) receives x_out in the activation dtype. */
+int llark_seq_add_rmsnorm(const float* x, const float* y, const float* w, float* x_out, void* x_act, long long rows, int C,
+                          float eps, int act_fp32, cudaStream_t stream);
+/* out[i] = rmsnorm(x[rows[i]]) * w in the activation dtype (rows == NULL: row i). */
+int llark_seq_rmsnorm_rows(const float* x, const int* rows, const float* w, void* out, int n_rows, int C, float eps,
+                           int act_fp32, cudaStream_t stream);
+int llark_seq_relu2(const void* u, void* y, long long n, int act_fp32, cudaStream_t stream);
+/* C[M,N] = A[M,K] W[N,K]^T (+ bias fp32[N]), fp32 accumulation, A / W bf16 or (in_fp32) float, C float if c_fp32.
+ * _rows: weight-streaming, for a handful of rows (decode). _simt: tiled, any shape, true fp32 when in_fp32. */
+int llark_linear_rows(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc, int c_fp32,
+                      const float* bias, int M, int N, int K, int in_fp32, cudaStream_t stream);
+int llark_linear_simt(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc, int c_fp32,
+                      const float* bias, int M, int N, int K, int in_fp32, cudaStream_t stream);
+/* Per-head RMS norm of the q (H heads at column q_off) and k (G heads at k_off) parts of src fp32 [n_tok, ld] with
+ * weights wq, wk fp32 [D]: qn [n_tok, H, D], kn [n_tok, G, D], vraw = the un-normed k. kring / vring non-NULL: also
+ * written to ring entry position % cap of the request's slot (only when every request brings one token). */
+int llark_seq_qk_headnorm(const float* src, long long ld, int q_off, int k_off, const float* wq, const float* wk, void* qn,
+                          void* kn, void* vraw, void* kring, void* vring, const int* tok_seq, const int* cu,
+                          const int* pos0, const int* slot, int n_tok, int H, int G, int D, int cap, float eps,
+                          int act_fp32, cudaStream_t stream);
+/* Sliding-window softmax attention: query at position i sees keys j with 0 <= i - j < window. Keys / values of this
+ * step come from kn / vv ([n_tok, G, D] / [n_tok, G, E]), earlier ones from the rings [slots, cap, G, D|E] (entry
+ * j % cap); from_ring_only = 1: the step's own token is already in the ring. score = q.k * scale_h[h]; the output is
+ * multiplied by sigmoid(gate[t, h*E + e]) when gate != NULL. out [n_tok, H, E]. */
+int llark_seq_swa_attn(const void* qn, const void* kn, const void* vv, const void* kring, const void* vring,
+                       const float* gate, long long gate_ld, const float* scale_h, void* out, const int* tok_seq,
+                       const int* cu, const int* pos0, const int* slot, int n_tok, int H, int G, int D, int E, int window,
+                       int cap, int from_ring_only, int act_fp32, cudaStream_t stream);
+int llark_seq_kv_ring_write(const void* kn, const void* vv, void* kring, void* vring, const int* tok_seq, const int* cu,
+                            const int* pos0, const int* slot, int n_tok, int GD, int GE, int cap, int act_fp32,
+                            cudaStream_t stream);
+/* Gated linear recurrence over src fp32 [n_tok, ld] (q_pre at q_off, f_pre incl. bias at f_off: H*D columns each; v at
+ * v_off: H*E columns): q = silu(q_pre), f = lower + (1 - lower) * sigmoid(f_pre) (lower fp32 [H*D] or NULL = 0),
+ * S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T q_t. state fp32 [slots, H, D, E] is read and written back;
+ * o_raw fp32 [n_tok, H*E]. D <= 256. */
+int llark_seq_glr_scan(const float* src, long long ld, int q_off, int f_off, int v_off, const float* lower, float* state,
+                       float* o_raw, const int* cu, const int* slot, int n_seq, int H, int D, int E, cudaStream_t stream);
+int llark_seq_head_rmsnorm(const float* x, const float* w, void* out, long long n_rows, int E, float eps, int act_fp32,
+                           cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

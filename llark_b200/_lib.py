@@ -9,9 +9,20 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 # LLARK_LIB_PATH: A/B perf experiments against another build of the same C-ABI (tools/); never a fallback
 LIB_PATH = os.environ.get("LLARK_LIB_PATH") or os.path.join(_HERE, "libllark_b200.so")
+# `make serve`: the subset of the library the generation path of native checkpoints needs (GEMM core, decode linears,
+# seq_* ops); used when the full library has not been built. Not a fallback for anything else: ops outside it raise.
+SERVE_LIB_PATH = os.path.join(_HERE, "libllark_serve.so")
 
 _ERR = {-1: "LLARK_EINVAL (bad shape/alignment/argument)", -2: "LLARK_ECUDA", -3: "LLARK_EDRIVER", -4: "LLARK_ENCCL"}
 
+# the generation path of layer-list decoders (csrc/seq_ops.cu, csrc/seq_mixers.cu)
+SEQ_SYMBOLS = [
+    "llark_seq_embed", "llark_seq_short_conv", "llark_seq_conv_tail", "llark_seq_add_rmsnorm", "llark_seq_rmsnorm_rows",
+    "llark_seq_relu2", "llark_linear_rows", "llark_linear_simt", "llark_seq_qk_headnorm", "llark_seq_swa_attn",
+    "llark_seq_kv_ring_write", "llark_seq_glr_scan", "llark_seq_head_rmsnorm",
+]
+# what libllark_serve.so (`make serve`: GEMM core + decode linears + the ops above) exports
+SERVE_SYMBOLS = SEQ_SYMBOLS + ["llark_last_cuda_error", "llark_init", "llark_gemm", "llark_gemm_ex", "llark_gemv"]
 # every symbol include/llark_b200.h declares (tests check that the library exports all of them)
 SYMBOLS = [
     "llark_last_cuda_error", "llark_gemm", "llark_gemm_ex", "llark_gemm_clear_cache", "llark_gemm_set_mode", "llark_gemm_get_mode", "llark_splice_scan", "llark_embed_splice_fwd",
@@ -26,7 +37,7 @@ SYMBOLS = [
     "llark_quick_gelu", "llark_add3", "llark_jb_pool", "llark_jb_pool_batched", "llark_colsum",
     "llark_init", "llark_attn_bwd_rope", "llark_jb_label_cond", "llark_v32_split_tf32", "llark_v32_embed_splice_fwd", "llark_v32_rmsnorm_fwd", "llark_v32_rope",
     "llark_v32_swiglu_fwd", "llark_v32_attn_fwd", "llark_v32_ce_fwd",
-]
+] + SEQ_SYMBOLS
 
 _lib = None
 
@@ -48,14 +59,17 @@ def lib():
     """Return the loaded CDLL; raises if the CUDA extension has not been built (no fallback path exists)."""
     global _lib
     if _lib is None:
-        if not os.path.exists(LIB_PATH):
+        path, subset = LIB_PATH, False
+        if not os.path.exists(path) and not os.environ.get("LLARK_LIB_PATH") and os.path.exists(SERVE_LIB_PATH):
+            path, subset = SERVE_LIB_PATH, True
+        if not os.path.exists(path):
             raise LlarkError(
                 f"{LIB_PATH} is missing: build the sm_100a extension first "
                 "(python -c 'import __graft_entry__ as g; g.build()'). llark_b200 has no CPU/PyTorch fallback."
             )
         import torch  # noqa: F401  (loads the NCCL / CUDA runtime libraries the extension resolves against)
 
-        _lib = ctypes.CDLL(LIB_PATH)
+        _lib = ctypes.CDLL(path)
         c = ctypes
         P, LL, I, F = c.c_void_p, c.c_longlong, c.c_int, c.c_float
         sig = {
@@ -120,10 +134,23 @@ def lib():
             "llark_v32_swiglu_fwd": ([P, P, LL, I, P], I),
             "llark_v32_attn_fwd": ([P, P, P, I, I, I, I, F, P], I),
             "llark_v32_ce_fwd": ([P, LL, I, P, I, I, P, P, P], I),
+            "llark_seq_embed": ([P, P, P, P, P, P, F, P, I, I, I, P], I),
+            "llark_seq_short_conv": ([P, P, P, P, P, P, P, I, I, I, I, I, P], I),
+            "llark_seq_conv_tail": ([P, P, P, P, I, I, I, P], I),
+            "llark_seq_add_rmsnorm": ([P, P, P, P, P, LL, I, F, I, P], I),
+            "llark_seq_rmsnorm_rows": ([P, P, P, P, I, I, F, I, P], I),
+            "llark_seq_relu2": ([P, P, LL, I, P], I),
+            "llark_linear_rows": ([P, LL, P, LL, P, LL, I, P, I, I, I, I, P], I),
+            "llark_linear_simt": ([P, LL, P, LL, P, LL, I, P, I, I, I, I, P], I),
+            "llark_seq_qk_headnorm": ([P, LL, I, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, I, P], I),
+            "llark_seq_swa_attn": ([P, P, P, P, P, P, LL, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P], I),
+            "llark_seq_kv_ring_write": ([P, P, P, P, P, P, P, P, I, I, I, I, I, P], I),
+            "llark_seq_glr_scan": ([P, LL, I, I, I, P, P, P, P, P, I, I, I, I, P], I),
+            "llark_seq_head_rmsnorm": ([P, P, P, LL, I, F, I, P], I),
         }
         for name, (argtypes, restype) in sig.items():
-            if os.environ.get("LLARK_LIB_PATH") and not hasattr(_lib, name):
-                continue  # A/B run against an older build of the C-ABI: newer entry points are simply absent
+            if (os.environ.get("LLARK_LIB_PATH") or subset) and not hasattr(_lib, name):
+                continue  # A/B run against an older build of the C-ABI, or the serve subset: the entry point is absent
             fn = getattr(_lib, name)
             fn.argtypes = argtypes
             fn.restype = restype

@@ -1,0 +1,420 @@
+// Sequence mixers of the generation path for layer-list decoders, on the packed-step layout of seq_ops.cu (tok_seq, cu,
+// pos0, slot). Every mixer keeps its per-request memory in a store indexed by slot, reads what earlier steps left there
+// and leaves what later steps need, so a whole prompt, a portion of one and a single decoded token are the same launch.
+//
+//   llark_seq_qk_headnorm   per-head RMS norm of the q and k columns of a fused projection; the raw k is kept as well
+//                           (designs whose values are the un-normed keys); optionally writes the ring directly (decode)
+//   llark_seq_swa_attn      softmax attention over a sliding window: keys of this step from the step's buffers, older
+//                           ones from the per-slot ring of the last `cap` positions; per-head score scale; optional
+//                           sigmoid output gate; scores, softmax and accumulation in fp32
+//   llark_seq_kv_ring_write stores the step's keys / values into the ring (after attention has read the old entries)
+//   llark_seq_glr_scan      gated linear recurrence S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T q_t with
+//                           f = low + (1 - low) * sigmoid(f_pre), q = silu(q_pre); fp32 state [slot, H, D, E]
+//   llark_seq_head_rmsnorm  per-head RMS norm of the recurrence's output
+#include "common.cuh"
+
+namespace llark {
+extern thread_local int g_last_cuda_error;
+namespace seqmix {
+
+static int check_launch() {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        g_last_cuda_error = (int)e;
+        return LLARK_ECUDA;
+    }
+    return LLARK_OK;
+}
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+// ------------------------------------------------------------------------------------------------ q / k head norm
+// src [n_tok, ld] fp32 with q heads at column q_off and k heads at k_off. Warp per (token, head).
+template <typename T>
+__global__ void qk_headnorm_kernel(const float* __restrict__ src, long long ld, int q_off, int k_off,
+                                   const float* __restrict__ wq, const float* __restrict__ wk, T* __restrict__ qn,
+                                   T* __restrict__ kn, T* __restrict__ vraw, T* __restrict__ kring, T* __restrict__ vring,
+                                   const int* __restrict__ tok_seq, const int* __restrict__ cu,
+                                   const int* __restrict__ pos0, const int* __restrict__ slot, int H, int G, int D,
+                                   int cap, float eps) {
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int hh = warp; hh < H + G; hh += nw) {
+        const bool is_q = hh < H;
+        const int head = is_q ? hh : hh - H;
+        const float* s = src + (long long)t * ld + (is_q ? q_off : k_off) + head * D;
+        float ss = 0.f;
+        for (int d = lane; d < D; d += 32) ss = fmaf(s[d], s[d], ss);
+        ss = warp_sum(ss);
+        const float r = 1.0f / sqrtf(ss / (float)D + eps);
+        const float* w = is_q ? wq : wk;
+        if (is_q) {
+            T* o = qn + ((long long)t * H + head) * D;
+            for (int d = lane; d < D; d += 32) stf(o + d, s[d] * r * w[d]);
+        } else {
+            T* o = kn + ((long long)t * G + head) * D;
+            T* ov = vraw + ((long long)t * G + head) * D;
+            T *rk = nullptr, *rv = nullptr;
+            if (kring) {  // one token per request: the entry it replaces is already outside the window
+                const int b = tok_seq[t];
+                const long long p = pos0[b] + (t - cu[b]);
+                const long long e = ((long long)slot[b] * cap + (p % cap)) * G + head;
+                rk = kring + e * D;
+                rv = vring + e * D;
+            }
+            for (int d = lane; d < D; d += 32) {
+                const float kv = s[d] * r * w[d];
+                stf(o + d, kv);
+                stf(ov + d, s[d]);
+                if (rk) {
+                    stf(rk + d, kv);
+                    stf(rv + d, s[d]);
+                }
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ windowed attention
+// Block per (token, head); its warps take the 32-key tiles of the window round-robin, each with its own online softmax,
+// and are merged at the end. Lane = key while scoring, lane = output channel while accumulating. DPL = ceil(E / 32).
+template <typename T, int DPL>
+__global__ void swa_attn_kernel(const T* __restrict__ qn, const T* __restrict__ kn, const T* __restrict__ vv,
+                                const T* __restrict__ kring, const T* __restrict__ vring, const float* __restrict__ gate,
+                                long long gate_ld, const float* __restrict__ scale_h, T* __restrict__ out,
+                                const int* __restrict__ tok_seq, const int* __restrict__ cu,
+                                const int* __restrict__ pos0, const int* __restrict__ slot, int H, int G, int D, int E,
+                                int window, int cap, int from_ring_only) {
+    extern __shared__ float sm[];
+    const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* sq = sm;                      // [D]
+    float* sp = sq + D;                  // [nw][32]
+    float* sm_m = sp + nw * 32;          // [nw]
+    float* sm_l = sm_m + nw;             // [nw]
+    float* sacc = sm_l + nw;             // [nw][E]
+    const int t = blockIdx.x, h = blockIdx.y;
+    const int g = h / (H / G);
+    const int b = tok_seq[t];
+    const long long p0 = pos0[b];
+    const long long p = p0 + (t - cu[b]);
+    const long long lo = p - window + 1 > 0 ? p - window + 1 : 0;
+    const int nkeys = (int)(p - lo + 1);
+    const float sc = scale_h[h];
+    for (int d = threadIdx.x; d < D; d += blockDim.x) sq[d] = ldf(qn + ((long long)t * H + h) * D + d);
+    __syncthreads();
+    const long long ring_base = (long long)slot[b] * cap;
+    const long long first_here = from_ring_only ? p + 1 : p0;  // positions >= first_here are rows of this step
+    float m = -INFINITY, l = 0.f, acc[DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
+    for (int tile = warp; tile * 32 < nkeys; tile += nw) {
+        const int jj = tile * 32 + lane;
+        const long long j = lo + jj;
+        float s = -INFINITY;
+        if (jj < nkeys) {
+            const T* kr = j >= first_here ? kn + ((long long)(cu[b] + (j - p0)) * G + g) * D
+                                          : kring + ((ring_base + (j % cap)) * G + g) * D;
+            float dot = 0.f;
+            for (int d = 0; d < D; ++d) dot = fmaf(sq[d], ldf(kr + d), dot);
+            s = dot * sc;
+        }
+        const float mt = warp_max(s);
+        const float mn = fmaxf(m, mt);
+        const float corr = expf(m - mn);  // m = -inf on the first tile: exp(-inf) = 0
+        const float pj = jj < nkeys ? expf(s - mn) : 0.f;
+        l = l * corr + warp_sum(pj);
+        m = mn;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) acc[i] *= corr;
+        sp[warp * 32 + lane] = pj;
+        __syncwarp();
+        const int cnt = nkeys - tile * 32 < 32 ? nkeys - tile * 32 : 32;
+        for (int k = 0; k < cnt; ++k) {
+            const long long j2 = lo + tile * 32 + k;
+            const T* vr = j2 >= first_here ? vv + ((long long)(cu[b] + (j2 - p0)) * G + g) * E
+                                           : vring + ((ring_base + (j2 % cap)) * G + g) * E;
+            const float pk = sp[warp * 32 + k];
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) {
+                const int e = lane + 32 * i;
+                if (e < E) acc[i] = fmaf(pk, ldf(vr + e), acc[i]);
+            }
+        }
+        __syncwarp();
+    }
+    if (lane == 0) {
+        sm_m[warp] = m;
+        sm_l[warp] = l;
+    }
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) {
+        const int e = lane + 32 * i;
+        if (e < E) sacc[warp * E + e] = acc[i];
+    }
+    __syncthreads();
+    float mm = -INFINITY;
+    for (int w = 0; w < nw; ++w) mm = fmaxf(mm, sm_m[w]);
+    float lt = 0.f;
+    for (int w = 0; w < nw; ++w) lt += sm_m[w] == -INFINITY ? 0.f : sm_l[w] * expf(sm_m[w] - mm);
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        float o = 0.f;
+        for (int w = 0; w < nw; ++w)
+            if (sm_m[w] != -INFINITY) o = fmaf(sacc[w * E + e], expf(sm_m[w] - mm), o);
+        o /= lt;
+        if (gate) o *= sigmoidf_(gate[(long long)t * gate_ld + h * E + e]);
+        stf(out + ((long long)t * H + h) * E + e, o);
+    }
+}
+
+template <typename T>
+__global__ void kv_ring_write_kernel(const T* __restrict__ kn, const T* __restrict__ vv, T* __restrict__ kring,
+                                     T* __restrict__ vring, const int* __restrict__ tok_seq,
+                                     const int* __restrict__ cu, const int* __restrict__ pos0,
+                                     const int* __restrict__ slot, int GD, int GE, int cap) {
+    const int t = blockIdx.x;
+    const int b = tok_seq[t];
+    const int local = t - cu[b], n = cu[b + 1] - cu[b];
+    if (n - 1 - local >= cap) return;  // an older row of this step that a later one replaces
+    const long long p = pos0[b] + local;
+    const long long e = (long long)slot[b] * cap + (p % cap);
+    for (int d = threadIdx.x; d < GD; d += blockDim.x) kring[e * GD + d] = kn[(long long)t * GD + d];
+    for (int d = threadIdx.x; d < GE; d += blockDim.x) vring[e * GE + d] = vv[(long long)t * GE + d];
+}
+
+// ------------------------------------------------------------------------------------------------ gated linear recurrence
+// Block per (E-slice, head, request). Thread (ec, r) owns rows d = r * DPT .. r * DPT + DPT - 1 of column e of S in
+// registers; R threads (adjacent lanes) share a column and add their partial outputs by shuffle. The inputs of TS steps
+// are brought to shared memory with cp.async while the previous TS steps are computed, and the gate arithmetic is done
+// once per element there.
+constexpr int kTS = 16;
+
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+template <int DPT>
+__global__ void glr_scan_kernel(const float* __restrict__ src, long long ld, int q_off, int f_off, int v_off,
+                                const float* __restrict__ lower, float* __restrict__ state, float* __restrict__ o_raw,
+                                const int* __restrict__ cu, const int* __restrict__ slot, int H, int D, int E, int R,
+                                int ecols) {
+    extern __shared__ float sm[];
+    constexpr int DPS = DPT + 1;  // padded row-group stride: the R groups of a column hit different banks
+    const int DP = R * DPS;
+    const int stage_floats = kTS * (3 * DP + ecols);
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int r = threadIdx.x % R, ec = threadIdx.x / R;
+    const int e = blockIdx.x * ecols + ec;
+    const int row0 = cu[b], n = cu[b + 1] - row0;
+    float* st = state + ((long long)slot[b] * H + h) * (long long)D * E;
+    float S[DPT];
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+        const int d = r * DPT + i;
+        S[i] = (d < D && e < E) ? st[(long long)d * E + e] : 0.f;
+    }
+    const int nstage = (n + kTS - 1) / kTS;
+    // stage layout: q[kTS][DP] | f[kTS][DP] | g[kTS][DP] | v[kTS][ecols]; raw q_pre / f_pre land in q / f
+    auto issue = [&](int s, float* buf) {
+        const int steps = n - s * kTS < kTS ? n - s * kTS : kTS;
+        for (int i = threadIdx.x; i < steps * D; i += blockDim.x) {
+            const int ts = i / D, d = i % D;
+            const float* rowp = src + (long long)(row0 + s * kTS + ts) * ld;
+            const int at = ts * DP + (d / DPT) * DPS + (d % DPT);
+            cp_async4(buf + at, rowp + q_off + h * D + d);
+            cp_async4(buf + kTS * DP + at, rowp + f_off + h * D + d);
+        }
+        for (int i = threadIdx.x; i < steps * ecols; i += blockDim.x) {
+            const int ts = i / ecols, c = i % ecols;
+            const int ee = blockIdx.x * ecols + c;
+            if (ee < E)
+                cp_async4(buf + 3 * kTS * DP + ts * ecols + c,
+                          src + (long long)(row0 + s * kTS + ts) * ld + v_off + h * E + ee);
+        }
+        cp_async_commit();
+    };
+    if (nstage > 0) issue(0, sm);
+    for (int s = 0; s < nstage; ++s) {
+        float* buf = sm + (s & 1) * stage_floats;
+        const int steps = n - s * kTS < kTS ? n - s * kTS : kTS;
+        cp_async_wait_all();
+        __syncthreads();  // stage s has landed; everybody is done computing stage s - 1 (the other buffer)
+        if (s + 1 < nstage) issue(s + 1, sm + ((s + 1) & 1) * stage_floats);
+        for (int i = threadIdx.x; i < steps * R * DPT; i += blockDim.x) {
+            const int ts = i / (R * DPT), d = i % (R * DPT);
+            const int at = ts * DP + (d / DPT) * DPS + (d % DPT);
+            float q = 0.f, f = 0.f, g = 0.f;
+            if (d < D) {
+                const float qp = buf[at], fp = buf[kTS * DP + at];
+                q = qp * sigmoidf_(qp);
+                const float lowv = lower ? lower[h * D + d] : 0.f;
+                f = lowv + (1.0f - lowv) * sigmoidf_(fp);
+                g = 1.0f - f;
+            }
+            buf[at] = q;
+            buf[kTS * DP + at] = f;
+            buf[2 * kTS * DP + at] = g;
+        }
+        __syncthreads();
+        for (int ts = 0; ts < steps; ++ts) {
+            const float vt = e < E ? buf[3 * kTS * DP + ts * ecols + ec] : 0.f;
+            const float* q = buf + ts * DP + r * DPS;
+            const float* f = q + kTS * DP;
+            const float* g = f + kTS * DP;
+            float part = 0.f;
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) {
+                S[i] = fmaf(f[i], S[i], g[i] * vt);
+                part = fmaf(S[i], q[i], part);
+            }
+            for (int o = R >> 1; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+            if (r == 0 && e < E) o_raw[(long long)(row0 + s * kTS + ts) * ((long long)H * E) + h * E + e] = part;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+        const int d = r * DPT + i;
+        if (d < D && e < E) st[(long long)d * E + e] = S[i];
+    }
+}
+
+template <typename T>
+__global__ void head_rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, T* __restrict__ out,
+                                    long long n_rows, int E, float eps) {
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= n_rows) return;
+    const float* xr = x + row * E;
+    float ss = 0.f;
+    for (int e = lane; e < E; e += 32) ss = fmaf(xr[e], xr[e], ss);
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss / (float)E + eps);
+    for (int e = lane; e < E; e += 32) stf(out + row * E + e, xr[e] * r * w[e]);
+}
+
+}  // namespace seqmix
+}  // namespace llark
+
+using namespace llark;
+using namespace llark::seqmix;
+typedef __nv_bfloat16 bf16_t;
+
+extern "C" int llark_seq_qk_headnorm(const float* src, long long ld, int q_off, int k_off, const float* wq,
+                                     const float* wk, void* qn, void* kn, void* vraw, void* kring, void* vring,
+                                     const int* tok_seq, const int* cu, const int* pos0, const int* slot, int n_tok, int H,
+                                     int G, int D, int cap, float eps, int act_fp32, cudaStream_t st) {
+    if (n_tok <= 0 || H <= 0 || G <= 0 || D <= 0 || !src || !wq || !wk || !qn || !kn || !vraw) return LLARK_EINVAL;
+    if (kring && (!vring || cap <= 0 || !tok_seq || !cu || !pos0 || !slot)) return LLARK_EINVAL;
+    int warps = H + G < 8 ? H + G : 8;
+    if (act_fp32)
+        qk_headnorm_kernel<float><<<n_tok, warps * 32, 0, st>>>(src, ld, q_off, k_off, wq, wk, (float*)qn, (float*)kn,
+                                                                (float*)vraw, (float*)kring, (float*)vring, tok_seq, cu,
+                                                                pos0, slot, H, G, D, cap, eps);
+    else
+        qk_headnorm_kernel<bf16_t><<<n_tok, warps * 32, 0, st>>>(src, ld, q_off, k_off, wq, wk, (bf16_t*)qn, (bf16_t*)kn,
+                                                                 (bf16_t*)vraw, (bf16_t*)kring, (bf16_t*)vring, tok_seq,
+                                                                 cu, pos0, slot, H, G, D, cap, eps);
+    return check_launch();
+}
+
+template <typename T>
+static int launch_swa(const void* qn, const void* kn, const void* vv, const void* kring, const void* vring,
+                      const float* gate, long long gate_ld, const float* scale_h, void* out, const int* tok_seq,
+                      const int* cu, const int* pos0, const int* slot, int n_tok, int H, int G, int D, int E, int window,
+                      int cap, int from_ring_only, cudaStream_t st) {
+    int nw = 1;
+    while (nw < 8 && nw * 64 < window) nw <<= 1;  // two tiles per warp before another warp pays off
+    const size_t smem = sizeof(float) * (size_t)(D + nw * 32 + 2 * nw + nw * E);
+    dim3 grid(n_tok, H);
+    const int dpl = (E + 31) / 32;
+#define LLARK_SWA(DPL)                                                                                              \
+    swa_attn_kernel<T, DPL><<<grid, nw * 32, smem, st>>>((const T*)qn, (const T*)kn, (const T*)vv, (const T*)kring, \
+                                                         (const T*)vring, gate, gate_ld, scale_h, (T*)out, tok_seq, \
+                                                         cu, pos0, slot, H, G, D, E, window, cap, from_ring_only)
+    if (dpl <= 1) LLARK_SWA(1);
+    else if (dpl <= 2) LLARK_SWA(2);
+    else if (dpl <= 4) LLARK_SWA(4);
+    else if (dpl <= 8) LLARK_SWA(8);
+    else return LLARK_EINVAL;
+#undef LLARK_SWA
+    return check_launch();
+}
+
+extern "C" int llark_seq_swa_attn(const void* qn, const void* kn, const void* vv, const void* kring, const void* vring,
+                                  const float* gate, long long gate_ld, const float* scale_h, void* out,
+                                  const int* tok_seq, const int* cu, const int* pos0, const int* slot, int n_tok, int H,
+                                  int G, int D, int E, int window, int cap, int from_ring_only, int act_fp32,
+                                  cudaStream_t st) {
+    if (n_tok <= 0 || H <= 0 || G <= 0 || (H % G) || D <= 0 || E <= 0 || window <= 0 || cap <= 0 || !qn || !kring ||
+        !vring || !scale_h || !out || !tok_seq || !cu || !pos0 || !slot)
+        return LLARK_EINVAL;
+    if (!from_ring_only && (!kn || !vv)) return LLARK_EINVAL;
+    if ((size_t)(D + 8 * 32 + 16 + 8 * E) * sizeof(float) > 48 * 1024) return LLARK_EINVAL;
+    return act_fp32 ? launch_swa<float>(qn, kn, vv, kring, vring, gate, gate_ld, scale_h, out, tok_seq, cu, pos0, slot,
+                                        n_tok, H, G, D, E, window, cap, from_ring_only, st)
+                    : launch_swa<bf16_t>(qn, kn, vv, kring, vring, gate, gate_ld, scale_h, out, tok_seq, cu, pos0, slot,
+                                         n_tok, H, G, D, E, window, cap, from_ring_only, st);
+}
+
+extern "C" int llark_seq_kv_ring_write(const void* kn, const void* vv, void* kring, void* vring, const int* tok_seq,
+                                       const int* cu, const int* pos0, const int* slot, int n_tok, int GD, int GE, int cap,
+                                       int act_fp32, cudaStream_t st) {
+    if (n_tok <= 0 || GD <= 0 || GE <= 0 || cap <= 0 || !kn || !vv || !kring || !vring) return LLARK_EINVAL;
+    if (act_fp32)
+        kv_ring_write_kernel<float><<<n_tok, 128, 0, st>>>((const float*)kn, (const float*)vv, (float*)kring,
+                                                           (float*)vring, tok_seq, cu, pos0, slot, GD, GE, cap);
+    else
+        kv_ring_write_kernel<bf16_t><<<n_tok, 128, 0, st>>>((const bf16_t*)kn, (const bf16_t*)vv, (bf16_t*)kring,
+                                                            (bf16_t*)vring, tok_seq, cu, pos0, slot, GD, GE, cap);
+    return check_launch();
+}
+
+extern "C" int llark_seq_glr_scan(const float* src, long long ld, int q_off, int f_off, int v_off, const float* lower,
+                                  float* state, float* o_raw, const int* cu, const int* slot, int n_seq, int H, int D,
+                                  int E, cudaStream_t st) {
+    if (n_seq <= 0 || H <= 0 || D <= 0 || E <= 0 || !src || !state || !o_raw || !cu || !slot) return LLARK_EINVAL;
+    if (D > 256) return LLARK_EINVAL;
+    const int dpt = D <= 128 ? 16 : 32;
+    int R = 1;
+    while (R * dpt < D) R <<= 1;  // 1, 2, 4 or 8 row groups: a power of two for the shuffle tree
+    int threads = 128;
+    int ecols = threads / R;
+    while (ecols / 2 >= E && threads > 32) {  // narrow heads: do not carry idle columns
+        threads >>= 1;
+        ecols >>= 1;
+    }
+    const int DP = R * (dpt + 1);
+    const size_t smem = sizeof(float) * 2 * (size_t)kTS * (3 * DP + ecols);
+    dim3 grid((E + ecols - 1) / ecols, H, n_seq);
+    if (dpt == 16) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(glr_scan_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        glr_scan_kernel<16><<<grid, threads, smem, st>>>(src, ld, q_off, f_off, v_off, lower, state, o_raw, cu, slot, H, D,
+                                                         E, R, ecols);
+    } else {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(glr_scan_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        glr_scan_kernel<32><<<grid, threads, smem, st>>>(src, ld, q_off, f_off, v_off, lower, state, o_raw, cu, slot, H, D,
+                                                         E, R, ecols);
+    }
+    return check_launch();
+}
+
+extern "C" int llark_seq_head_rmsnorm(const float* x, const float* w, void* out, long long n_rows, int E, float eps,
+                                      int act_fp32, cudaStream_t st) {
+    if (n_rows <= 0 || E <= 0 || !x || !w || !out) return LLARK_EINVAL;
+    const unsigned grid = (unsigned)((n_rows + 3) / 4);
+    if (act_fp32)
+        head_rmsnorm_kernel<float><<<grid, 128, 0, st>>>(x, w, (float*)out, n_rows, E, eps);
+    else
+        head_rmsnorm_kernel<bf16_t><<<grid, 128, 0, st>>>(x, w, (bf16_t*)out, n_rows, E, eps);
+    return check_launch();
+}

@@ -1,0 +1,363 @@
+// Token-major ops of the generation path for layer-list decoders (Kelutar and whatever else is assembled from the
+// same parts). One step of the engine is a PACKED batch: the new tokens of all requests concatenated, [Ttot, width],
+// no padding; `tok_seq[t]` names the request of token t, `cu[b]` its first row, `pos0[b]` the position of that row in
+// its sequence and `slot[b]` the request's row in every state store. A request that starts, goes on by a portion of
+// its prompt, or decodes one token is the same launch with other numbers.
+//
+// Precision: the residual stream, every norm and the convolution state are fp32. `ACT` is the activation / matrix
+// dtype: bf16 when serving, float in the all-fp32 mode (act_fp32 = 1), where the linears run on the SIMT kernels below
+// in true fp32 (no TF32).
+//
+//   llark_seq_embed         x = table[id] * scale + pos_table[position]
+//   llark_seq_short_conv    y = h + causal depthwise conv(h) with carry-in of the last taps-1 inputs per request
+//   llark_seq_conv_tail     refresh of that carry after a step of more than one token per request
+//   llark_seq_add_rmsnorm   x_out = x + rmsnorm(y) * w   (norm on the sublayer's output), optional ACT copy of x_out
+//   llark_seq_rmsnorm_rows  y[i] = rmsnorm(x[rows[i]]) * w -> ACT (final norm of the rows whose logits are wanted)
+//   llark_seq_relu2         y = relu(u)^2
+//   llark_linear_rows       C = A W^T (+ bias) for a handful of rows: weight-streaming, one warp per output column
+//   llark_linear_simt       C = A W^T (+ bias), any shape, tiled SIMT with fp32 accumulation (the fp32 mode's GEMM and the
+//                           fallback for shapes the TMA descriptors of the tcgen05 core cannot take)
+#include "common.cuh"
+
+namespace llark {
+extern thread_local int g_last_cuda_error;
+namespace seq {
+
+static int check_launch() {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        g_last_cuda_error = (int)e;
+        return LLARK_ECUDA;
+    }
+    return LLARK_OK;
+}
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    v = warp_sum(v);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (l == 0) red[w] = v;
+    __syncthreads();
+    float s = 0.f;
+    for (int i = 0; i < nw; ++i) s += red[i];
+    return s;
+}
+
+// ------------------------------------------------------------------------------------------------ embedding
+template <typename T>
+__global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict__ tok_seq, const int* __restrict__ cu,
+                             const int* __restrict__ pos0, const T* __restrict__ table, const T* __restrict__ pos_table,
+                             float scale, float* __restrict__ x, int C) {
+    const int t = blockIdx.x;
+    const int b = tok_seq[t];
+    const long long p = pos0[b] + (t - cu[b]);
+    const T* e = table + (long long)ids[t] * C;
+    const T* pe = pos_table ? pos_table + p * C : nullptr;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float v = ldf(e + c) * scale;
+        if (pe) v += ldf(pe + c);
+        x[(long long)t * C + c] = v;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ short convolution
+// y[t, c] = h[t, c] + sum_j w[c, j] * h[t - taps + 1 + j, c]; inputs before this step's first row come from
+// tail[slot][k][c], k = 0 .. taps-2 oldest first (zeros for a fresh request). inline_tail: every request brings exactly
+// one token and the thread that read the carry also shifts it.
+template <typename T>
+__global__ void short_conv_kernel(const float* __restrict__ h, const float* __restrict__ w, float* __restrict__ tail,
+                                  const int* __restrict__ tok_seq, const int* __restrict__ cu,
+                                  const int* __restrict__ slot, T* __restrict__ y, int C, int taps, int inline_tail) {
+    const int t = blockIdx.x;
+    const int b = tok_seq[t];
+    const int local = t - cu[b];
+    float* tl = tail + (long long)slot[b] * (taps - 1) * C;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        const float cur = h[(long long)t * C + c];
+        float acc = w[c * taps + taps - 1] * cur;
+        for (int j = 0; j < taps - 1; ++j) {
+            const int s = local - taps + 1 + j;
+            const float v = s >= 0 ? h[(long long)(t - local + s) * C + c] : tl[(long long)(taps - 1 + s) * C + c];
+            acc = fmaf(w[c * taps + j], v, acc);
+        }
+        stf(y + (long long)t * C + c, cur + acc);
+        if (inline_tail) {
+            for (int k = 0; k + 1 < taps - 1; ++k) tl[(long long)k * C + c] = tl[(long long)(k + 1) * C + c];
+            if (taps > 1) tl[(long long)(taps - 2) * C + c] = cur;
+        }
+    }
+}
+
+// new tail[k] = input at local index n - (taps-1) + k (from this step's rows, or from the old tail when negative)
+__global__ void conv_tail_kernel(const float* __restrict__ h, float* __restrict__ tail, const int* __restrict__ cu,
+                                 const int* __restrict__ slot, int C, int taps) {
+    const int b = blockIdx.x;
+    const int r0 = cu[b], n = cu[b + 1] - r0;
+    float* tl = tail + (long long)slot[b] * (taps - 1) * C;
+    for (int c = threadIdx.x; c < C; c += blockDim.x)
+        for (int k = 0; k < taps - 1; ++k) {  // ascending k: an old entry is read at index k + n >= k before it is rewritten
+            const int s = n - (taps - 1) + k;
+            tl[(long long)k * C + c] = s >= 0 ? h[(long long)(r0 + s) * C + c] : tl[(long long)(taps - 1 + s) * C + c];
+        }
+}
+
+// ------------------------------------------------------------------------------------------------ norms
+template <typename T>
+__global__ void add_rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ w,
+                                   float* __restrict__ x_out, T* __restrict__ x_act, int C, float eps) {
+    __shared__ float red[32];
+    const long long row = blockIdx.x;
+    const float* yr = y + row * C;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) ss = fmaf(yr[c], yr[c], ss);
+    ss = block_sum(ss, red);
+    const float r = 1.0f / sqrtf(ss / (float)C + eps);
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        const float v = x[row * C + c] + yr[c] * r * w[c];
+        x_out[row * C + c] = v;
+        if (x_act) stf(x_act + row * C + c, v);
+    }
+}
+
+template <typename T>
+__global__ void rmsnorm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
+                                    T* __restrict__ out, int C, float eps) {
+    __shared__ float red[32];
+    const long long src = rows ? rows[blockIdx.x] : blockIdx.x;
+    const float* xr = x + src * C;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) ss = fmaf(xr[c], xr[c], ss);
+    ss = block_sum(ss, red);
+    const float r = 1.0f / sqrtf(ss / (float)C + eps);
+    for (int c = threadIdx.x; c < C; c += blockDim.x) stf(out + (long long)blockIdx.x * C + c, xr[c] * r * w[c]);
+}
+
+template <typename T>
+__global__ void relu2_kernel(const T* __restrict__ u, T* __restrict__ y, long long n) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float v = fmaxf(ldf(u + i), 0.f);
+        stf(y + i, v * v);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ linears
+// Few rows (decode): warp per output column, lanes stride over K, the rows of A come from L1 / L2.
+template <typename T, typename TC, int MB>
+__global__ void __launch_bounds__(256)
+linear_rows_kernel(const T* __restrict__ A, long long lda, const T* __restrict__ W, long long ldw, TC* __restrict__ Cm,
+                   long long ldc, const float* __restrict__ bias, int M, int N, int K, int vec_ok) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long n = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+    const int m0 = blockIdx.y * MB;
+    if (n >= N) return;
+    float acc[MB];
+#pragma unroll
+    for (int m = 0; m < MB; ++m) acc[m] = 0.f;
+    const T* wr = W + n * ldw;
+    constexpr int VEC = 16 / (int)sizeof(T);
+    int k0 = 0;
+    if (vec_ok) {
+        const int kv = K / VEC;
+        for (int v = lane; v < kv; v += 32) {
+            const uint4 wv = __ldcs(reinterpret_cast<const uint4*>(wr) + v);
+            const T* wp = reinterpret_cast<const T*>(&wv);
+#pragma unroll
+            for (int m = 0; m < MB; ++m) {
+                if (m0 + m < M) {
+                    const uint4 av = __ldg(reinterpret_cast<const uint4*>(A + (long long)(m0 + m) * lda) + v);
+                    const T* ap = reinterpret_cast<const T*>(&av);
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) acc[m] = fmaf(ldf(ap + e), ldf(wp + e), acc[m]);
+                }
+            }
+        }
+        k0 = kv * VEC;
+    }
+    for (int k = k0 + lane; k < K; k += 32) {
+        const float wv = ldf(wr + k);
+#pragma unroll
+        for (int m = 0; m < MB; ++m)
+            if (m0 + m < M) acc[m] = fmaf(ldf(A + (long long)(m0 + m) * lda + k), wv, acc[m]);
+    }
+#pragma unroll
+    for (int m = 0; m < MB; ++m) {
+        const float s = warp_sum(acc[m]);
+        if (lane == 0 && m0 + m < M) stf(Cm + (long long)(m0 + m) * ldc + n, s + (bias ? bias[n] : 0.f));
+    }
+}
+
+// Any shape: 64 x 64 tile, 16-deep k slices through shared memory, 4 x 4 outputs per thread, fp32 FMA.
+template <typename T, typename TC>
+__global__ void __launch_bounds__(256)
+linear_simt_kernel(const T* __restrict__ A, long long lda, const T* __restrict__ W, long long ldw, TC* __restrict__ Cm,
+                   long long ldc, const float* __restrict__ bias, int M, int N, int K) {
+    constexpr int BM = 64, BN = 64, BK = 16;
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Ws[BK][BN + 4];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        for (int i = threadIdx.x; i < BM * BK; i += 256) {
+            const int r = i / BK, k = i % BK;
+            As[k][r] = (m0 + r < M && k0 + k < K) ? ldf(A + (long long)(m0 + r) * lda + k0 + k) : 0.f;
+            Ws[k][r] = (n0 + r < N && k0 + k < K) ? ldf(W + (long long)(n0 + r) * ldw + k0 + k) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < BK; ++k) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[k][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) b[j] = Ws[k][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+            if (m < M && n < N) stf(Cm + (long long)m * ldc + n, acc[i][j] + (bias ? bias[n] : 0.f));
+        }
+}
+
+static int norm_threads(int C) {
+    int t = 32;
+    while (t < C / 4 && t < 512) t <<= 1;
+    return t;
+}
+
+}  // namespace seq
+}  // namespace llark
+
+using namespace llark;
+using namespace llark::seq;
+typedef __nv_bfloat16 bf16_t;
+
+extern "C" int llark_seq_embed(const int* ids, const int* tok_seq, const int* cu, const int* pos0, const void* table,
+                               const void* pos_table, float scale, float* x, int n_tok, int C, int act_fp32,
+                               cudaStream_t st) {
+    if (n_tok <= 0 || C <= 0 || !ids || !tok_seq || !cu || !pos0 || !table || !x) return LLARK_EINVAL;
+    const int th = norm_threads(C);
+    if (act_fp32)
+        embed_kernel<float><<<n_tok, th, 0, st>>>(ids, tok_seq, cu, pos0, (const float*)table, (const float*)pos_table,
+                                                  scale, x, C);
+    else
+        embed_kernel<bf16_t><<<n_tok, th, 0, st>>>(ids, tok_seq, cu, pos0, (const bf16_t*)table,
+                                                   (const bf16_t*)pos_table, scale, x, C);
+    return check_launch();
+}
+
+extern "C" int llark_seq_short_conv(const float* h, const float* w, float* tail, const int* tok_seq, const int* cu,
+                                    const int* slot, void* y, int n_tok, int C, int taps, int inline_tail, int act_fp32,
+                                    cudaStream_t st) {
+    if (n_tok <= 0 || C <= 0 || taps < 1 || !h || !w || !y || (taps > 1 && !tail)) return LLARK_EINVAL;
+    const int th = norm_threads(C);
+    if (act_fp32)
+        short_conv_kernel<float><<<n_tok, th, 0, st>>>(h, w, tail, tok_seq, cu, slot, (float*)y, C, taps, inline_tail);
+    else
+        short_conv_kernel<bf16_t><<<n_tok, th, 0, st>>>(h, w, tail, tok_seq, cu, slot, (bf16_t*)y, C, taps, inline_tail);
+    return check_launch();
+}
+
+extern "C" int llark_seq_conv_tail(const float* h, float* tail, const int* cu, const int* slot, int n_seq, int C,
+                                   int taps, cudaStream_t st) {
+    if (n_seq <= 0 || C <= 0 || taps < 1 || !h) return LLARK_EINVAL;
+    if (taps == 1) return LLARK_OK;
+    conv_tail_kernel<<<n_seq, norm_threads(C), 0, st>>>(h, tail, cu, slot, C, taps);
+    return check_launch();
+}
+
+extern "C" int llark_seq_add_rmsnorm(const float* x, const float* y, const float* w, float* x_out, void* x_act,
+                                     long long rows, int C, float eps, int act_fp32, cudaStream_t st) {
+    if (rows <= 0 || C <= 0 || !x || !y || !w || !x_out) return LLARK_EINVAL;
+    const int th = norm_threads(C);
+    if (act_fp32)
+        add_rmsnorm_kernel<float><<<(unsigned)rows, th, 0, st>>>(x, y, w, x_out, (float*)x_act, C, eps);
+    else
+        add_rmsnorm_kernel<bf16_t><<<(unsigned)rows, th, 0, st>>>(x, y, w, x_out, (bf16_t*)x_act, C, eps);
+    return check_launch();
+}
+
+extern "C" int llark_seq_rmsnorm_rows(const float* x, const int* rows, const float* w, void* out, int n_rows, int C,
+                                      float eps, int act_fp32, cudaStream_t st) {
+    if (n_rows <= 0 || C <= 0 || !x || !w || !out) return LLARK_EINVAL;
+    const int th = norm_threads(C);
+    if (act_fp32)
+        rmsnorm_rows_kernel<float><<<n_rows, th, 0, st>>>(x, rows, w, (float*)out, C, eps);
+    else
+        rmsnorm_rows_kernel<bf16_t><<<n_rows, th, 0, st>>>(x, rows, w, (bf16_t*)out, C, eps);
+    return check_launch();
+}
+
+extern "C" int llark_seq_relu2(const void* u, void* y, long long n, int act_fp32, cudaStream_t st) {
+    if (n <= 0 || !u || !y) return LLARK_EINVAL;
+    const unsigned grid = (unsigned)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    if (act_fp32)
+        relu2_kernel<float><<<grid, 256, 0, st>>>((const float*)u, (float*)y, n);
+    else
+        relu2_kernel<bf16_t><<<grid, 256, 0, st>>>((const bf16_t*)u, (bf16_t*)y, n);
+    return check_launch();
+}
+
+template <typename T, typename TC>
+static void launch_rows(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc,
+                        const float* bias, int M, int N, int K, cudaStream_t st) {
+    const int vec = 16 / (int)sizeof(T);
+    const int vec_ok = (K % vec == 0) && (lda % vec == 0) && (ldw % vec == 0) &&
+                       (((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) == 0);
+    const int warps = 8;
+    const unsigned gx = (unsigned)((N + warps - 1) / warps);
+    if (M <= 2) {
+        dim3 grid(gx, (M + 1) / 2);
+        linear_rows_kernel<T, TC, 2><<<grid, warps * 32, 0, st>>>((const T*)A, lda, (const T*)W, ldw, (TC*)C, ldc, bias, M,
+                                                                  N, K, vec_ok);
+    } else {
+        dim3 grid(gx, (M + 7) / 8);
+        linear_rows_kernel<T, TC, 8><<<grid, warps * 32, 0, st>>>((const T*)A, lda, (const T*)W, ldw, (TC*)C, ldc, bias, M,
+                                                                  N, K, vec_ok);
+    }
+}
+
+extern "C" int llark_linear_rows(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc,
+                                 int c_fp32, const float* bias, int M, int N, int K, int in_fp32, cudaStream_t st) {
+    if (M <= 0 || N <= 0 || K <= 0 || !A || !W || !C || lda < K || ldw < K || ldc < N) return LLARK_EINVAL;
+    if (in_fp32 && !c_fp32) return LLARK_EINVAL;
+    if (in_fp32)
+        launch_rows<float, float>(A, lda, W, ldw, C, ldc, bias, M, N, K, st);
+    else if (c_fp32)
+        launch_rows<bf16_t, float>(A, lda, W, ldw, C, ldc, bias, M, N, K, st);
+    else
+        launch_rows<bf16_t, bf16_t>(A, lda, W, ldw, C, ldc, bias, M, N, K, st);
+    return check_launch();
+}
+
+extern "C" int llark_linear_simt(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc,
+                                 int c_fp32, const float* bias, int M, int N, int K, int in_fp32, cudaStream_t st) {
+    if (M <= 0 || N <= 0 || K <= 0 || !A || !W || !C || lda < K || ldw < K || ldc < N) return LLARK_EINVAL;
+    if (in_fp32 && !c_fp32) return LLARK_EINVAL;
+    dim3 grid((N + 63) / 64, (M + 63) / 64);
+    if (in_fp32)
+        linear_simt_kernel<float, float><<<grid, 256, 0, st>>>((const float*)A, lda, (const float*)W, ldw, (float*)C, ldc,
+                                                               bias, M, N, K);
+    else if (c_fp32)
+        linear_simt_kernel<bf16_t, float><<<grid, 256, 0, st>>>((const bf16_t*)A, lda, (const bf16_t*)W, ldw, (float*)C,
+                                                                ldc, bias, M, N, K);
+    else
+        linear_simt_kernel<bf16_t, bf16_t><<<grid, 256, 0, st>>>((const bf16_t*)A, lda, (const bf16_t*)W, ldw, (bf16_t*)C,
+                                                                 ldc, bias, M, N, K);
+    return check_launch();
+}

@@ -465,3 +465,148 @@ def v32_ce_fwd(logits, V, labels, B, S):
     check(lib().llark_v32_ce_fwd(_p(_f32(logits)), logits.stride(0), V, _p(labels), B, S, _p(row_loss), _p(loss_out),
                                  _stream()), "v32_ce_fwd")
     return loss_out[0]
+
+
+# ------------------------------------------------------------------------------------------------ generation path of
+# layer-list decoders (csrc/seq_ops.cu, csrc/seq_mixers.cu). `st` is a llark_b200.state_cache.StepLayout: the packed
+# step (tok_seq, cu, pos0, slot on the device). The residual stream is fp32; `act` is torch.bfloat16 or torch.float32.
+def _actf(dtype):
+    if dtype not in (BF16, torch.float32):
+        raise TypeError(f"activation dtype must be bfloat16 or float32, got {dtype}")
+    return int(dtype == torch.float32)
+
+
+# rows up to which a linear is the weight-streaming kernel (the activations then sit in L1 / L2, the op is a pure read
+# of the weight matrix); above it the tcgen05 GEMM core (bf16) or the tiled SIMT kernel (fp32 mode, odd shapes)
+LINEAR_ROWS_MAX = 8
+LINEAR_STATS = {"rows": 0, "tcgen05": 0, "simt": 0}
+
+
+def linear(a, w, bias=None, out_dtype=None, out=None):
+    """y[M, N] = a[M, K] @ w[N, K]^T (+ bias fp32 [N]); a and w both bf16 or both fp32 (true fp32 arithmetic, no TF32);
+    output bf16 or fp32."""
+    _req(a), _req(w)
+    if a.dtype != w.dtype:
+        raise TypeError("linear: activation and weight dtypes differ")
+    in_fp32 = _actf(a.dtype)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise ValueError("linear: inner sizes differ")
+    if out is None:
+        out = torch.empty((M, N), device=a.device, dtype=out_dtype or a.dtype)
+    c_fp32 = _actf(out.dtype)
+    if bias is not None:
+        _req(bias, torch.float32)
+    vec = 4 if c_fp32 else 8
+    if M <= LINEAR_ROWS_MAX:
+        LINEAR_STATS["rows"] += 1
+        check(lib().llark_linear_rows(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), c_fp32, _p(bias),
+                                      M, N, K, in_fp32, _stream()), "linear_rows")
+    elif (not in_fp32 and K % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and out.stride(0) % vec == 0
+          and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0):
+        LINEAR_STATS["tcgen05"] += 1
+        gemm(a, w, bias=bias, out=out, M=M, N=N, K=K)
+    else:
+        LINEAR_STATS["simt"] += 1
+        check(lib().llark_linear_simt(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), c_fp32, _p(bias),
+                                      M, N, K, in_fp32, _stream()), "linear_simt")
+    return out
+
+
+def seq_embed(ids, st, table, pos_table, scale):
+    """ids int32 [n_tok] -> x fp32 [n_tok, C] = table[id] * scale + pos_table[position]."""
+    _req(ids, torch.int32)
+    C = table.shape[1]
+    x = torch.empty((st.n_tok, C), device=table.device, dtype=torch.float32)
+    check(lib().llark_seq_embed(_p(ids), _p(st.tok_seq), _p(st.cu), _p(st.pos0), _p(table), _p(pos_table), float(scale),
+                                _p(x), st.n_tok, C, _actf(table.dtype), _stream()), "seq_embed")
+    return x
+
+
+def seq_short_conv(h, w, tail, st, act):
+    """h fp32 [n_tok, C], w fp32 [C, taps], tail fp32 [slots, taps-1, C] (updated) -> h + conv(h) in `act`."""
+    _req(h, torch.float32), _req(w, torch.float32)
+    C, taps = w.shape
+    y = torch.empty((st.n_tok, C), device=h.device, dtype=act)
+    inline = int(st.max_len == 1)
+    check(lib().llark_seq_short_conv(_p(h), _p(w), _p(tail), _p(st.tok_seq), _p(st.cu), _p(st.slot), _p(y), st.n_tok, C,
+                                     taps, inline, _actf(act), _stream()), "seq_short_conv")
+    if not inline and taps > 1:
+        check(lib().llark_seq_conv_tail(_p(h), _p(tail), _p(st.cu), _p(st.slot), st.n_seq, C, taps, _stream()),
+              "seq_conv_tail")
+    return y
+
+
+def seq_add_rmsnorm(x, y, w, eps, act=None):
+    """x + rmsnorm(y) * w (fp32, new tensor); with `act` also a copy of the result in that dtype."""
+    _req(x, torch.float32), _req(y, torch.float32), _req(w, torch.float32)
+    rows, C = x.shape
+    out = torch.empty_like(x)
+    xa = torch.empty((rows, C), device=x.device, dtype=act) if act is not None else None
+    check(lib().llark_seq_add_rmsnorm(_p(x), _p(y), _p(w), _p(out), _p(xa), rows, C, float(eps),
+                                      _actf(act) if act is not None else 0, _stream()), "seq_add_rmsnorm")
+    return (out, xa) if act is not None else out
+
+
+def seq_rmsnorm_rows(x, rows, w, eps, act):
+    _req(x, torch.float32), _req(w, torch.float32)
+    n = rows.numel() if rows is not None else x.shape[0]
+    C = x.shape[1]
+    out = torch.empty((n, C), device=x.device, dtype=act)
+    check(lib().llark_seq_rmsnorm_rows(_p(x), _p(rows), _p(w), _p(out), n, C, float(eps), _actf(act), _stream()),
+          "seq_rmsnorm_rows")
+    return out
+
+
+def seq_relu2(u):
+    y = torch.empty_like(u)
+    check(lib().llark_seq_relu2(_p(u), _p(y), u.numel(), _actf(u.dtype), _stream()), "seq_relu2")
+    return y
+
+
+def seq_qk_headnorm(src, q_off, k_off, wq, wk, H, G, D, eps, act, st=None, kring=None, vring=None, cap=0):
+    """src fp32 [n_tok, ld] -> (qn [n_tok, H*D], kn [n_tok, G*D], vraw [n_tok, G*D]) in `act`; with kring / vring the
+    k rows also go straight into the rings (steps of one token per request)."""
+    _req(src, torch.float32)
+    n = src.shape[0]
+    qn = torch.empty((n, H * D), device=src.device, dtype=act)
+    kn = torch.empty((n, G * D), device=src.device, dtype=act)
+    vr = torch.empty((n, G * D), device=src.device, dtype=act)
+    check(lib().llark_seq_qk_headnorm(_p(src), src.stride(0), q_off, k_off, _p(wq), _p(wk), _p(qn), _p(kn), _p(vr),
+                                      _p(kring), _p(vring), _p(st.tok_seq) if st else None, _p(st.cu) if st else None,
+                                      _p(st.pos0) if st else None, _p(st.slot) if st else None, n, H, G, D, cap,
+                                      float(eps), _actf(act), _stream()), "seq_qk_headnorm")
+    return qn, kn, vr
+
+
+def seq_swa_attn(qn, kn, vv, kring, vring, gate, gate_ld, scale_h, st, H, G, D, E, window, cap, from_ring_only):
+    out = torch.empty((st.n_tok, H * E), device=qn.device, dtype=qn.dtype)
+    check(lib().llark_seq_swa_attn(_p(qn), _p(kn), _p(vv), _p(kring), _p(vring), _p(gate), gate_ld, _p(scale_h), _p(out),
+                                   _p(st.tok_seq), _p(st.cu), _p(st.pos0), _p(st.slot), st.n_tok, H, G, D, E, window, cap,
+                                   int(from_ring_only), _actf(qn.dtype), _stream()), "seq_swa_attn")
+    return out
+
+
+def seq_kv_ring_write(kn, vv, kring, vring, st, cap):
+    check(lib().llark_seq_kv_ring_write(_p(kn), _p(vv), _p(kring), _p(vring), _p(st.tok_seq), _p(st.cu), _p(st.pos0),
+                                        _p(st.slot), st.n_tok, kn.shape[1], vv.shape[1], cap, _actf(kn.dtype), _stream()),
+          "seq_kv_ring_write")
+
+
+def seq_glr_scan(src, q_off, f_off, v_off, lower, state, st, H, D, E):
+    """src fp32 [n_tok, ld] -> o_raw fp32 [n_tok, H*E]; state fp32 [slots, H, D, E] read and written back."""
+    _req(src, torch.float32), _req(state, torch.float32)
+    o = torch.empty((st.n_tok, H * E), device=src.device, dtype=torch.float32)
+    check(lib().llark_seq_glr_scan(_p(src), src.stride(0), q_off, f_off, v_off, _p(lower), _p(state), _p(o), _p(st.cu),
+                                   _p(st.slot), st.n_seq, H, D, E, _stream()), "seq_glr_scan")
+    return o
+
+
+def seq_head_rmsnorm(x, w, E, eps, act):
+    """x fp32 [n_tok, H*E]: RMS norm of every E-wide head with the shared weight w fp32 [E] -> `act`."""
+    _req(x, torch.float32)
+    out = torch.empty(x.shape, device=x.device, dtype=act)
+    check(lib().llark_seq_head_rmsnorm(_p(x), _p(w), _p(out), x.numel() // E, E, float(eps), _actf(act), _stream()),
+          "seq_head_rmsnorm")
+    return out
