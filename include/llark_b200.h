@@ -311,15 +311,31 @@ int llark_seq_swa_attn(const void* qn, const void* kn, const void* vv, const voi
                        const float* gate, long long gate_ld, const float* scale_h, void* out, const int* tok_seq,
                        const int* cu, const int* pos0, const int* slot, int n_tok, int H, int G, int D, int E, int window,
                        int cap, int from_ring_only, int act_fp32, cudaStream_t stream);
+/* The same attention for steps that bring many tokens per request (prompts, portions): bf16 only, D = E a multiple of
+ * 16 up to 256, 64-query CTAs on mma.sync with fp32 scores / softmax (csrc/seq_swa_mma.cu). max_len = the longest
+ * request of the step. */
+int llark_seq_swa_attn_mma(const void* qn, const void* kn, const void* vv, const void* kring, const void* vring,
+                           const float* gate, long long gate_ld, const float* scale_h, void* out, const int* cu,
+                           const int* pos0, const int* slot, int n_seq, int max_len, int H, int G, int D, int window,
+                           int cap, cudaStream_t stream);
 int llark_seq_kv_ring_write(const void* kn, const void* vv, void* kring, void* vring, const int* tok_seq, const int* cu,
                             const int* pos0, const int* slot, int n_tok, int GD, int GE, int cap, int act_fp32,
                             cudaStream_t stream);
 /* Gated linear recurrence over src fp32 [n_tok, ld] (q_pre at q_off, f_pre incl. bias at f_off: H*D columns each; v at
  * v_off: H*E columns): q = silu(q_pre), f = lower + (1 - lower) * sigmoid(f_pre) (lower fp32 [H*D] or NULL = 0),
- * S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T q_t. state fp32 [slots, H, D, E] is read and written back;
- * o_raw fp32 [n_tok, H*E]. D <= 256. */
-int llark_seq_glr_scan(const float* src, long long ld, int q_off, int f_off, int v_off, const float* lower, float* state,
-                       float* o_raw, const int* cu, const int* slot, int n_seq, int H, int D, int E, cudaStream_t stream);
+ * S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T q_t, all fp32, D <= 256. The rows are handed over as work items:
+ * item w covers rows item_row0[w] .. + item_n[w] of one request, starts from init_buf[item_init[w]] ([*, H, D, E]; -1:
+ * zero) and leaves its last state in final_buf[item_final[w]] (-1: nowhere). decay_buf (optional) [n_items, H, D] gets the
+ * product of the item's forget gates; o_raw (optional) fp32 [n_tok, H*E] the outputs. One pass with items = requests and
+ * init = final = the slot in the state store is the plain scan. Long prompts: pass 1 over chunks from zero (local states +
+ * decays, no outputs), llark_seq_glr_combine turns the local states into each chunk's starting state, pass 2 over the
+ * chunks from those writes the outputs and (last chunk) the request's state. */
+int llark_seq_glr_scan(const float* src, long long ld, int q_off, int f_off, int v_off, const float* lower,
+                       const float* init_buf, float* final_buf, float* decay_buf, float* o_raw, const int* item_row0,
+                       const int* item_n, const int* item_init, const int* item_final, int n_items, int H, int D, int E,
+                       cudaStream_t stream);
+int llark_seq_glr_combine(const float* state, float* chunk_state, const float* chunk_decay, const int* seq_item0,
+                          const int* slot, int n_seq, int H, int D, int E, cudaStream_t stream);
 int llark_seq_head_rmsnorm(const float* x, const float* w, void* out, long long n_rows, int E, float eps, int act_fp32,
                            cudaStream_t stream);
 

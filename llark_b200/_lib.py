@@ -19,7 +19,8 @@ _ERR = {-1: "LLARK_EINVAL (bad shape/alignment/argument)", -2: "LLARK_ECUDA", -3
 SEQ_SYMBOLS = [
     "llark_seq_embed", "llark_seq_short_conv", "llark_seq_conv_tail", "llark_seq_add_rmsnorm", "llark_seq_rmsnorm_rows",
     "llark_seq_relu2", "llark_linear_rows", "llark_linear_simt", "llark_seq_qk_headnorm", "llark_seq_swa_attn",
-    "llark_seq_kv_ring_write", "llark_seq_glr_scan", "llark_seq_head_rmsnorm",
+    "llark_seq_swa_attn_mma",
+    "llark_seq_kv_ring_write", "llark_seq_glr_scan", "llark_seq_glr_combine", "llark_seq_head_rmsnorm",
 ]
 # what libllark_serve.so (`make serve`: GEMM core + decode linears + the ops above) exports
 SERVE_SYMBOLS = SEQ_SYMBOLS + ["llark_last_cuda_error", "llark_init", "llark_gemm", "llark_gemm_ex", "llark_gemv"]
@@ -144,8 +145,10 @@ def lib():
             "llark_linear_simt": ([P, LL, P, LL, P, LL, I, P, I, I, I, I, P], I),
             "llark_seq_qk_headnorm": ([P, LL, I, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, I, P], I),
             "llark_seq_swa_attn": ([P, P, P, P, P, P, LL, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P], I),
+            "llark_seq_swa_attn_mma": ([P, P, P, P, P, P, LL, P, P, P, P, P, I, I, I, I, I, I, I, P], I),
             "llark_seq_kv_ring_write": ([P, P, P, P, P, P, P, P, I, I, I, I, I, P], I),
-            "llark_seq_glr_scan": ([P, LL, I, I, I, P, P, P, P, P, I, I, I, I, P], I),
+            "llark_seq_glr_scan": ([P, LL, I, I, I, P, P, P, P, P, P, P, P, P, I, I, I, I, P], I),
+            "llark_seq_glr_combine": ([P, P, P, P, P, I, I, I, I, P], I),
             "llark_seq_head_rmsnorm": ([P, P, P, LL, I, F, I, P], I),
         }
         for name, (argtypes, restype) in sig.items():

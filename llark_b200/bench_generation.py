@@ -1,0 +1,322 @@
+"""Generation throughput of the Kelutar path beside the Llama path at equal size (`bench.py --workload generation`).
+
+Random weights, synthetic token ids. For each size: prefill tokens/s (a packed batch of whole prompts) and decode tokens/s
+(one token per request and step, after a prompt of `context` tokens) for both decoders, plus a per-op table: every op
+of one prefill step and one decode step is bracketed by CUDA events on the launching stream (the ops module's functions
+are wrapped for the duration), its algorithmic bytes and FLOPs are counted from the shapes, and its distance from the
+roofline max(bytes / measured copy bandwidth, FLOPs / measured bf16 peak) is reported, so that each Kelutar kernel can be
+read against the like kernel of the Llama path. Timing: >= 3 warm-up steps, an L2 flush (a 256 MB fill) between timed
+steps, CUDA events, synchronised on both sides."""
+import json
+import math
+import os
+import time
+
+import torch
+
+BF16, F32 = torch.bfloat16, torch.float32
+
+# (name, width, layers, heads, head dim, window, ff, vocab): layers repeat hgrn2, hgrn2, hgrn2, attention(+ff)
+SIZES = [
+    ("w2048", 2048, 8, 16, 128, 1024, 8192, 32000),
+    ("w4096", 4096, 4, 32, 128, 2048, 11008, 32000),
+]
+
+
+def kelutar_config(width, layers, heads, dim, window, ff, vocab, max_positions):
+    ls = []
+    for i in range(layers):
+        if i % 4 == 3:
+            ls.append({"type": "attention", "mixer": {"heads": heads, "kv_heads": heads, "dim": dim, "vdim": dim,
+                                                      "mask": {"size": window}, "scale": 1.0 / math.sqrt(dim)},
+                       "mlp": {"kind": "dense", "ff": ff}})
+        else:
+            ls.append({"type": "hgrn2", "mixer": {"heads": heads, "dim": dim, "vdim": dim}, "mlp": None})
+    return {"architecture": "Kelutar", "vocab": vocab, "width": width, "max_positions": max_positions,
+            "embedding": {"scale": math.sqrt(width)}, "norm": {"eps": 1e-5}, "canon": {"taps": 4}, "layers": ls}
+
+
+def kelutar_random_weights(cfg, device, seed=0):
+    g = torch.Generator(device=device).manual_seed(seed)
+    C = cfg["width"]
+
+    def mat(o, i, s=None):
+        return (torch.randn(o, i, device=device, generator=g) * (s or 1.0 / math.sqrt(i))).to(BF16)
+
+    def vec(n, mean=1.0, s=0.1):
+        return (mean + torch.randn(n, device=device, generator=g) * s).to(BF16)
+
+    W = {"embed": mat(cfg["vocab"], C, 1.0 / math.sqrt(C)), "pos": mat(cfg["max_positions"], C, 0.5),
+         "final.norm": vec(C), "head": mat(cfg["vocab"], C)}
+    for i, layer in enumerate(cfg["layers"]):
+        p, m = "l%d." % i, layer["mixer"]
+        H, D = m["heads"], m["dim"]
+        W[p + "norm1"], W[p + "canon1"] = vec(C), mat(C, cfg["canon"]["taps"], 0.3)
+        if layer["type"] == "attention":
+            G = m["kv_heads"]
+            W.update({p + "mix.q": mat(H * D, C), p + "mix.q.b": vec(H * D, 0.0), p + "mix.k": mat(G * D, C),
+                      p + "mix.k.b": vec(G * D, 0.0), p + "mix.q.norm": vec(D), p + "mix.k.norm": vec(D),
+                      p + "mix.temp": vec(H), p + "mix.g": mat(H * D, C), p + "mix.o": mat(C, H * D)})
+        else:
+            E = m["vdim"]
+            W.update({p + "mix.q": mat(H * D, C), p + "mix.f": mat(H * D, C), p + "mix.v": mat(H * E, C),
+                      p + "mix.f.b": vec(H * D, 1.0, 1.0), p + "mix.lower": vec(H * D, 0.5, 0.1).clamp(0, 0.95),
+                      p + "mix.norm": vec(E), p + "mix.o": mat(C, H * E)})
+        if layer["mlp"] is not None:
+            F = layer["mlp"]["ff"]
+            W.update({p + "norm2": vec(C), p + "mlp.up": mat(F, C), p + "mlp.down": mat(C, F)})
+    return W
+
+
+def llama_model(width, layers, heads, ff, vocab, max_positions):
+    from llark_b200.models.llamav2 import WrappedLlamav2Config, WrappedLlamav2ForCausalLM
+
+    hf = WrappedLlamav2Config(hidden_size=width, intermediate_size=ff, num_hidden_layers=layers,
+                              num_attention_heads=heads, num_key_value_heads=heads, vocab_size=vocab,
+                              max_position_embeddings=max_positions, rms_norm_eps=1e-5)
+    hf.mm_hidden_size = 64
+    old = torch.get_default_dtype()
+    torch.set_default_dtype(BF16)
+    try:
+        with torch.device("cuda"):
+            model = WrappedLlamav2ForCausalLM(hf)
+    finally:
+        torch.set_default_dtype(old)
+    return model.to(BF16).eval()
+
+
+class _Flush:
+    def __init__(self):
+        self.buf = torch.empty(256 << 20, device="cuda", dtype=torch.uint8)
+
+    def __call__(self):
+        self.buf.fill_(1)
+
+
+def timed(fn, warmup, iters, flush, setup=None):
+    """Median ms of fn() over iters, each after setup() and an L2 flush, CUDA events on the current stream."""
+    ms = []
+    for i in range(warmup + iters):
+        if setup is not None:
+            setup()
+        flush()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= warmup:
+            ms.append(e0.elapsed_time(e1))
+    ms.sort()
+    return ms[len(ms) // 2]
+
+
+class OpTimer:
+    """Wraps the named functions of llark_b200.ops with CUDA-event brackets while active."""
+
+    def __init__(self, names):
+        from llark_b200 import ops
+
+        self.ops, self.names, self.saved, self.records = ops, names, {}, []
+
+    def __enter__(self):
+        for n in self.names:
+            f = getattr(self.ops, n)
+            self.saved[n] = f
+
+            def wrap(*a, __f=f, __n=n, **k):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                out = __f(*a, **k)
+                e1.record()
+                self.records.append((__n, e0, e1, a, k, out))
+                return out
+
+            setattr(self.ops, n, wrap)
+        return self
+
+    def __exit__(self, *exc):
+        for n, f in self.saved.items():
+            setattr(self.ops, n, f)
+        torch.cuda.synchronize()
+
+
+def _nbytes(x):
+    if torch.is_tensor(x):
+        return x.numel() * x.element_size()
+    if isinstance(x, (tuple, list)):
+        return sum(_nbytes(y) for y in x)
+    return 0
+
+
+def _work(name, a, k, out, ctx):
+    """(algorithmic bytes, FLOPs) of one recorded call. Stores that are only partly touched (rings, states, KV caches)
+    are counted by what the op has to read and write, the rest by the tensors handed in and out."""
+    if name in ("linear", "gemm", "gemv"):
+        x, w = a[0], a[1]
+        M, K = x.shape[0], x.shape[1]
+        N = k.get("N") or w.shape[0]
+        return _nbytes(x) + N * K * w.element_size() + _nbytes(out), 2.0 * M * N * K
+    if name == "seq_swa_attn":
+        qn, st, H, G, D, E, window = a[0], a[8], a[9], a[10], a[11], a[12], a[13]
+        keys = sum(min(window, p0 + i + 1) for p0, n in zip(st.pos0_host, st.lens) for i in range(n))
+        kv_once = sum(min(n + min(window, p0), n + window) for p0, n in zip(st.pos0_host, st.lens)) * G * (D + E) * 2
+        return 2 * _nbytes(qn) + kv_once + st.n_tok * H * E * 4, 2.0 * keys * H * (D + E)
+    if name == "attn_fwd":
+        qkv, B, S, NH, D = a[0], a[2], a[3], a[4], a[5]
+        return _nbytes(qkv) + B * S * NH * D * 2, 4.0 * B * NH * D * S * (S + 1) / 2
+    if name == "attn_decode":
+        q, lens_ctx = a[0], ctx["context"]
+        B, H = q.shape
+        return 2 * B * lens_ctx * H * 2 + 2 * _nbytes(q), 4.0 * B * lens_ctx * H
+    if name == "seq_glr_scan":
+        src, state, st, H, D, E = a[0], a[5], a[6], a[7], a[8], a[9]
+        return _nbytes(src) + 2 * st.n_seq * H * D * E * 4 + st.n_tok * H * E * 4, 5.0 * st.n_tok * H * D * E
+    if name == "seq_short_conv":
+        return _nbytes(a[0]) + _nbytes(out), 0.0
+    if name == "seq_qk_headnorm":
+        return _nbytes(a[0]) * 2 // 3 + _nbytes(out), 0.0
+    if name == "seq_kv_ring_write":
+        return 2 * (_nbytes(a[0]) + _nbytes(a[1])), 0.0
+    if name == "embed_splice_fwd":
+        return 2 * _nbytes(a[6]), 0.0
+    if name == "seq_embed":
+        return 3 * _nbytes(out), 0.0
+    if name == "rope_":
+        return 2 * _nbytes(a[0]) * 2 // 3, 0.0
+    tensors = [x for x in a if torch.is_tensor(x)] + [v for v in k.values() if torch.is_tensor(v)]
+    return sum(_nbytes(t) for t in tensors) + (_nbytes(out) if not any(out is t for t in tensors) else 0), 0.0
+
+
+def op_table(records, ctx, peaks):
+    bw, fl = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    agg = {}
+    for name, e0, e1, a, k, out in records:
+        if name == "gemm" and ctx.get("skip_gemm"):
+            continue  # already inside `linear`
+        ms = e0.elapsed_time(e1)
+        nb, flops = _work(name, a, k, out, ctx)
+        if name == "linear":
+            name = "linear_rows" if a[0].shape[0] <= 8 else "linear_tcgen05"
+        if name == "gemm":
+            name = "gemm_tcgen05"
+        d = agg.setdefault(name, {"calls": 0, "ms": 0.0, "bytes": 0, "flops": 0.0, "roof_ms": 0.0})
+        d["calls"] += 1
+        d["ms"] += ms
+        d["bytes"] += nb
+        d["flops"] += flops
+        d["roof_ms"] += max(nb / bw, flops / fl) * 1e3
+    for d in agg.values():
+        d["of_roofline"] = round(d["roof_ms"] / d["ms"], 4) if d["ms"] > 0 else None
+        d["ms"], d["roof_ms"] = round(d["ms"], 4), round(d["roof_ms"], 4)
+        d["gb_s"] = round(d["bytes"] / (d["ms"] * 1e-3) / 1e9, 1) if d["ms"] > 0 else None
+        d["tflops"] = round(d["flops"] / (d["ms"] * 1e-3) / 1e12, 2) if d["ms"] > 0 else None
+        del d["bytes"], d["flops"]
+    return agg
+
+
+KELUTAR_OPS = ["linear", "seq_embed", "seq_short_conv", "seq_add_rmsnorm", "seq_rmsnorm_rows", "seq_relu2",
+               "seq_qk_headnorm", "seq_swa_attn", "seq_kv_ring_write", "seq_glr_scan", "seq_head_rmsnorm"]
+LLAMA_OPS = ["gemm", "gemv", "rmsnorm_fwd", "rope_", "attn_fwd", "attn_decode", "swiglu_fwd", "embed_splice_fwd"]
+
+
+def bench_size(name, width, layers, heads, dim, window, ff, vocab, peaks, steps, warmup, prefill_batch=4,
+               prompt=2048, decode_batches=(1, 8, 32), context=1024):
+    from llark_b200.models.kelutar import KelutarConfig, KelutarForCausalLM
+
+    flush = _Flush()
+    max_pos = max(prompt, context) + 64
+    out = {"size": name, "width": width, "layers": layers, "heads": heads, "head_dim": dim, "window": window, "ff": ff,
+           "vocab": vocab, "prefill": {"batch": prefill_batch, "prompt": prompt}, "decode": {"context": context}}
+    g = torch.Generator().manual_seed(0)
+    ids_prefill = torch.randint(0, vocab, (prefill_batch, prompt), generator=g)
+    # ------------------------------------------------------------------ Kelutar
+    cfg = kelutar_config(width, layers, heads, dim, window, ff, vocab, max_pos)
+    km = KelutarForCausalLM(KelutarConfig.from_dict(cfg), kelutar_random_weights(cfg, "cuda"), dtype=BF16)
+    eng = km.engine
+    state = {}
+
+    def k_setup_prefill():
+        state["cache"] = eng.new_cache(n_slots=prefill_batch)
+        state["slots"] = [state["cache"].alloc() for _ in range(prefill_batch)]
+
+    toks = ids_prefill.tolist()
+    ms = timed(lambda: eng.step(state["cache"], state["slots"], toks), warmup, steps, flush, setup=k_setup_prefill)
+    out["prefill"]["kelutar_tokens_per_s"] = round(prefill_batch * prompt / ms * 1e3, 1)
+    out["prefill"]["kelutar_ms"] = round(ms, 3)
+    for _ in range(2):  # the second pass is the one that is read: no first-use cost of the wrappers
+        k_setup_prefill()
+        with OpTimer(KELUTAR_OPS) as t:
+            eng.step(state["cache"], state["slots"], toks)
+    out["prefill"]["kelutar_ops"] = op_table(t.records, {}, peaks)
+    for B in decode_batches:
+        cache = eng.new_cache(n_slots=B)
+        slots = [cache.alloc() for _ in range(B)]
+        eng.step(cache, slots, torch.randint(0, vocab, (B, context), generator=g).tolist())
+        nxt = torch.randint(0, vocab, (B, 1), generator=g).tolist()
+        ms = timed(lambda: eng.step(cache, slots, nxt), warmup, max(steps, 10), flush)
+        out["decode"]["kelutar_b%d_tokens_per_s" % B] = round(B / ms * 1e3, 1)
+        out["decode"]["kelutar_b%d_ms" % B] = round(ms, 3)
+        if B == decode_batches[-1] or B == 8:
+            for _ in range(2):
+                with OpTimer(KELUTAR_OPS) as t:
+                    eng.step(cache, slots, nxt)
+            out["decode"]["kelutar_b%d_ops" % B] = op_table(t.records, {"context": context}, peaks)
+    del km, eng, cache
+    torch.cuda.empty_cache()
+    # ------------------------------------------------------------------ Llama path at equal size
+    lm = llama_model(width, layers, heads, ff, vocab, max_pos)
+    le = lm.engine
+    dev = torch.device("cuda")
+    ids_dev = ids_prefill.to(dev)
+
+    def l_setup_prefill():
+        state["lc"] = le.new_cache(prefill_batch, max_pos, dev)
+
+    ms = timed(lambda: le.prefill(ids_dev, None, state["lc"]), warmup, steps, flush, setup=l_setup_prefill)
+    out["prefill"]["llama_tokens_per_s"] = round(prefill_batch * prompt / ms * 1e3, 1)
+    out["prefill"]["llama_ms"] = round(ms, 3)
+    for _ in range(2):
+        l_setup_prefill()
+        with OpTimer(LLAMA_OPS) as t:
+            le.prefill(ids_dev, None, state["lc"])
+    out["prefill"]["llama_ops"] = op_table(t.records, {}, peaks)
+    for B in decode_batches:
+        lc = le.new_cache(B, max_pos, dev)
+        le.prefill(torch.randint(0, vocab, (B, context), generator=g).to(dev), None, lc)
+        nxt = torch.randint(0, vocab, (B, 1), generator=g).to(dev)
+
+        def l_step():
+            lc.length = context
+            le.decode_step(nxt, lc)
+
+        ms = timed(l_step, warmup, max(steps, 10), flush)
+        out["decode"]["llama_b%d_tokens_per_s" % B] = round(B / ms * 1e3, 1)
+        out["decode"]["llama_b%d_ms" % B] = round(ms, 3)
+        if B == decode_batches[-1] or B == 8:
+            for _ in range(2):
+                with OpTimer(LLAMA_OPS) as t:
+                    l_step()
+            out["decode"]["llama_b%d_ops" % B] = op_table(t.records, {"context": context}, peaks)
+    del lm, le, lc
+    torch.cuda.empty_cache()
+    return out
+
+
+def run(args, peaks, peaks_kind, emit):
+    from llark_b200 import ops
+
+    ops.init()
+    t0 = time.time()
+    sizes = [s for s in SIZES if not os.environ.get("LLARK_BENCH_SIZE") or s[0] == os.environ["LLARK_BENCH_SIZE"]]
+    results = [bench_size(*s, peaks=peaks, steps=args.steps, warmup=max(args.warmup, 3)) for s in sizes]
+    head = results[0]
+    emit({"metric": "generation tokens/s, Kelutar beside the Llama path at equal size (prefill of %d x %d tokens)"
+                    % (head["prefill"]["batch"], head["prefill"]["prompt"]),
+          "value": head["prefill"]["kelutar_tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+          "warmup": max(args.warmup, 3), "ms_per_step": head["prefill"]["kelutar_ms"], "higher_is_better": True,
+          "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, random weights",
+          "config": {"model": "Kelutar " + head["size"], "l2": "256 MB fill between timed steps",
+                     "peaks": peaks_kind, "hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"]},
+          "sizes": results, "wall_s": round(time.time() - t0, 1)})

@@ -19,7 +19,7 @@ def _sources_newer_than(lib, names):
     return any(os.path.exists(p) and os.path.getmtime(p) > t for p in paths)
 
 
-SERVE_SOURCES = ("gemm_tcgen05.cu", "gemv.cu", "seq_ops.cu", "seq_mixers.cu", "common.cuh")
+SERVE_SOURCES = ("gemm_tcgen05.cu", "gemv.cu", "seq_ops.cu", "seq_mixers.cu", "seq_swa_mma.cu", "common.cuh")
 
 
 def ensure_built(verbose=False):

@@ -9,7 +9,8 @@
 //                           sigmoid output gate; scores, softmax and accumulation in fp32
 //   llark_seq_kv_ring_write stores the step's keys / values into the ring (after attention has read the old entries)
 //   llark_seq_glr_scan      gated linear recurrence S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T q_t with
-//                           f = low + (1 - low) * sigmoid(f_pre), q = silu(q_pre); fp32 state [slot, H, D, E]
+//                           f = low + (1 - low) * sigmoid(f_pre), q = silu(q_pre); fp32 state [slot, H, D, E]; long
+//                           prompts run as chunks in three passes (local states, llark_seq_glr_combine, outputs)
 //   llark_seq_head_rmsnorm  per-head RMS norm of the recurrence's output
 #include "common.cuh"
 
@@ -201,11 +202,17 @@ __device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
+// A work item is a run of consecutive rows of one request: the whole step of the request (one pass: init = final = its
+// slot of the state store), or one chunk of a long prompt (three passes, see llark_seq_glr_scan). item_init / item_final
+// index init_buf / final_buf ([*, H, D, E]); -1 = start from zero / keep nothing. decay_buf (optional) [items, H, D]
+// receives the product of the item's forget gates per channel; o_raw may be NULL (no outputs wanted).
 template <int DPT>
 __global__ void glr_scan_kernel(const float* __restrict__ src, long long ld, int q_off, int f_off, int v_off,
-                                const float* __restrict__ lower, float* __restrict__ state, float* __restrict__ o_raw,
-                                const int* __restrict__ cu, const int* __restrict__ slot, int H, int D, int E, int R,
-                                int ecols) {
+                                const float* __restrict__ lower, const float* __restrict__ init_buf,
+                                float* __restrict__ final_buf, float* __restrict__ decay_buf, float* __restrict__ o_raw,
+                                const int* __restrict__ item_row0, const int* __restrict__ item_n,
+                                const int* __restrict__ item_init, const int* __restrict__ item_final, int H, int D,
+                                int E, int R, int ecols) {
     extern __shared__ float sm[];
     constexpr int DPS = DPT + 1;  // padded row-group stride: the R groups of a column hit different banks
     const int DP = R * DPS;
@@ -213,14 +220,19 @@ __global__ void glr_scan_kernel(const float* __restrict__ src, long long ld, int
     const int h = blockIdx.y, b = blockIdx.z;
     const int r = threadIdx.x % R, ec = threadIdx.x / R;
     const int e = blockIdx.x * ecols + ec;
-    const int row0 = cu[b], n = cu[b + 1] - row0;
-    float* st = state + ((long long)slot[b] * H + h) * (long long)D * E;
+    const int row0 = item_row0[b], n = item_n[b];
+    const int i_init = item_init[b], i_final = item_final[b];
+    const float* st_in = i_init >= 0 ? init_buf + ((long long)i_init * H + h) * (long long)D * E : nullptr;
     float S[DPT];
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
         const int d = r * DPT + i;
-        S[i] = (d < D && e < E) ? st[(long long)d * E + e] : 0.f;
+        S[i] = (st_in && d < D && e < E) ? st_in[(long long)d * E + e] : 0.f;
     }
+    const bool want_decay = decay_buf != nullptr && blockIdx.x == 0;
+    float decay[8];  // rows threadIdx.x + k * blockDim.x (8 * 32 >= the widest padded head)
+#pragma unroll
+    for (int k = 0; k < 8; ++k) decay[k] = 1.f;
     const int nstage = (n + kTS - 1) / kTS;
     // stage layout: q[kTS][DP] | f[kTS][DP] | g[kTS][DP] | v[kTS][ecols]; raw q_pre / f_pre land in q / f
     auto issue = [&](int s, float* buf) {
@@ -264,6 +276,14 @@ __global__ void glr_scan_kernel(const float* __restrict__ src, long long ld, int
             buf[2 * kTS * DP + at] = g;
         }
         __syncthreads();
+        if (want_decay) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int d = threadIdx.x + k * blockDim.x;
+                if (d < D)
+                    for (int ts = 0; ts < steps; ++ts) decay[k] *= buf[kTS * DP + ts * DP + (d / DPT) * DPS + (d % DPT)];
+            }
+        }
         for (int ts = 0; ts < steps; ++ts) {
             const float vt = e < E ? buf[3 * kTS * DP + ts * ecols + ec] : 0.f;
             const float* q = buf + ts * DP + r * DPS;
@@ -276,13 +296,44 @@ __global__ void glr_scan_kernel(const float* __restrict__ src, long long ld, int
                 part = fmaf(S[i], q[i], part);
             }
             for (int o = R >> 1; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-            if (r == 0 && e < E) o_raw[(long long)(row0 + s * kTS + ts) * ((long long)H * E) + h * E + e] = part;
+            if (o_raw && r == 0 && e < E) o_raw[(long long)(row0 + s * kTS + ts) * ((long long)H * E) + h * E + e] = part;
         }
     }
+    if (i_final >= 0) {
+        float* st_out = final_buf + ((long long)i_final * H + h) * (long long)D * E;
 #pragma unroll
-    for (int i = 0; i < DPT; ++i) {
-        const int d = r * DPT + i;
-        if (d < D && e < E) st[(long long)d * E + e] = S[i];
+        for (int i = 0; i < DPT; ++i) {
+            const int d = r * DPT + i;
+            if (d < D && e < E) st_out[(long long)d * E + e] = S[i];
+        }
+    }
+    if (want_decay) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int d = threadIdx.x + k * blockDim.x;
+            if (d < D) decay_buf[((long long)b * H + h) * D + d] = decay[k];
+        }
+    }
+}
+
+// Between the two chunk passes: walks the chunks of each request in order. On entry chunk_state[w] is the state chunk w
+// builds from zero and chunk_decay[w] the product of its forget gates; on exit chunk_state[w] is the state chunk w
+// STARTS from: S_in(first) = the request's stored state, S_in(w + 1) = diag(decay_w) S_in(w) + S_local(w).
+__global__ void glr_combine_kernel(const float* __restrict__ state, float* __restrict__ chunk_state,
+                                   const float* __restrict__ chunk_decay, const int* __restrict__ seq_item0,
+                                   const int* __restrict__ slot, int H, int D, int E) {
+    const int h = blockIdx.y, b = blockIdx.z;
+    const long long de = (long long)D * E;
+    const int w0 = seq_item0[b], w1 = seq_item0[b + 1];
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < de; i += (long long)gridDim.x * blockDim.x) {
+        const int d = (int)(i / E);
+        float S = state[((long long)slot[b] * H + h) * de + i];
+        for (int w = w0; w < w1; ++w) {
+            float* cs = chunk_state + ((long long)w * H + h) * de + i;
+            const float loc = *cs;
+            *cs = S;
+            S = fmaf(chunk_decay[((long long)w * H + h) * D + d], S, loc);
+        }
     }
 }
 
@@ -378,9 +429,11 @@ extern "C" int llark_seq_kv_ring_write(const void* kn, const void* vv, void* kri
 }
 
 extern "C" int llark_seq_glr_scan(const float* src, long long ld, int q_off, int f_off, int v_off, const float* lower,
-                                  float* state, float* o_raw, const int* cu, const int* slot, int n_seq, int H, int D,
-                                  int E, cudaStream_t st) {
-    if (n_seq <= 0 || H <= 0 || D <= 0 || E <= 0 || !src || !state || !o_raw || !cu || !slot) return LLARK_EINVAL;
+                                  const float* init_buf, float* final_buf, float* decay_buf, float* o_raw,
+                                  const int* item_row0, const int* item_n, const int* item_init, const int* item_final,
+                                  int n_items, int H, int D, int E, cudaStream_t st) {
+    if (n_items <= 0 || H <= 0 || D <= 0 || E <= 0 || !src || !item_row0 || !item_n || !item_init || !item_final)
+        return LLARK_EINVAL;
     if (D > 256) return LLARK_EINVAL;
     const int dpt = D <= 128 ? 16 : 32;
     int R = 1;
@@ -393,18 +446,31 @@ extern "C" int llark_seq_glr_scan(const float* src, long long ld, int q_off, int
     }
     const int DP = R * (dpt + 1);
     const size_t smem = sizeof(float) * 2 * (size_t)kTS * (3 * DP + ecols);
-    dim3 grid((E + ecols - 1) / ecols, H, n_seq);
+    dim3 grid((E + ecols - 1) / ecols, H, n_items);
     if (dpt == 16) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(glr_scan_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        glr_scan_kernel<16><<<grid, threads, smem, st>>>(src, ld, q_off, f_off, v_off, lower, state, o_raw, cu, slot, H, D,
+        glr_scan_kernel<16><<<grid, threads, smem, st>>>(src, ld, q_off, f_off, v_off, lower, init_buf, final_buf,
+                                                         decay_buf, o_raw, item_row0, item_n, item_init, item_final, H, D,
                                                          E, R, ecols);
     } else {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(glr_scan_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        glr_scan_kernel<32><<<grid, threads, smem, st>>>(src, ld, q_off, f_off, v_off, lower, state, o_raw, cu, slot, H, D,
+        glr_scan_kernel<32><<<grid, threads, smem, st>>>(src, ld, q_off, f_off, v_off, lower, init_buf, final_buf,
+                                                         decay_buf, o_raw, item_row0, item_n, item_init, item_final, H, D,
                                                          E, R, ecols);
     }
+    return check_launch();
+}
+
+extern "C" int llark_seq_glr_combine(const float* state, float* chunk_state, const float* chunk_decay,
+                                     const int* seq_item0, const int* slot, int n_seq, int H, int D, int E,
+                                     cudaStream_t st) {
+    if (n_seq <= 0 || H <= 0 || D <= 0 || E <= 0 || !state || !chunk_state || !chunk_decay || !seq_item0 || !slot)
+        return LLARK_EINVAL;
+    const long long de = (long long)D * E;
+    dim3 grid((unsigned)((de + 255) / 256), H, n_seq);
+    glr_combine_kernel<<<grid, 256, 0, st>>>(state, chunk_state, chunk_decay, seq_item0, slot, H, D, E);
     return check_launch();
 }
 

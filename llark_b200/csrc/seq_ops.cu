@@ -95,6 +95,43 @@ __global__ void short_conv_kernel(const float* __restrict__ h, const float* __re
     }
 }
 
+// The same with four channels per thread (C % 4 == 0): 16-byte loads of h and of the four channels' taps.
+template <typename T>
+__global__ void short_conv4_kernel(const float* __restrict__ h, const float* __restrict__ w, float* __restrict__ tail,
+                                   const int* __restrict__ tok_seq, const int* __restrict__ cu,
+                                   const int* __restrict__ slot, T* __restrict__ y, int C, int taps, int inline_tail) {
+    const int t = blockIdx.x;
+    const int b = tok_seq[t];
+    const int local = t - cu[b];
+    float* tl = tail + (long long)slot[b] * (taps - 1) * C;
+    for (int c = threadIdx.x * 4; c < C; c += blockDim.x * 4) {
+        const float4 cur = *reinterpret_cast<const float4*>(h + (long long)t * C + c);
+        const float* wc = w + (long long)c * taps;  // taps of channel c, then of c + 1, ...
+        float4 acc = make_float4(wc[taps - 1] * cur.x, wc[2 * taps - 1] * cur.y, wc[3 * taps - 1] * cur.z,
+                                 wc[4 * taps - 1] * cur.w);
+        for (int j = 0; j < taps - 1; ++j) {
+            const int s = local - taps + 1 + j;
+            const float4 v = *reinterpret_cast<const float4*>(
+                s >= 0 ? h + (long long)(t - local + s) * C + c : tl + (long long)(taps - 1 + s) * C + c);
+            acc.x = fmaf(wc[j], v.x, acc.x);
+            acc.y = fmaf(wc[taps + j], v.y, acc.y);
+            acc.z = fmaf(wc[2 * taps + j], v.z, acc.z);
+            acc.w = fmaf(wc[3 * taps + j], v.w, acc.w);
+        }
+        T* yo = y + (long long)t * C + c;
+        stf(yo, cur.x + acc.x);
+        stf(yo + 1, cur.y + acc.y);
+        stf(yo + 2, cur.z + acc.z);
+        stf(yo + 3, cur.w + acc.w);
+        if (inline_tail) {
+            for (int k = 0; k + 1 < taps - 1; ++k)
+                *reinterpret_cast<float4*>(tl + (long long)k * C + c) =
+                    *reinterpret_cast<const float4*>(tl + (long long)(k + 1) * C + c);
+            if (taps > 1) *reinterpret_cast<float4*>(tl + (long long)(taps - 2) * C + c) = cur;
+        }
+    }
+}
+
 // new tail[k] = input at local index n - (taps-1) + k (from this step's rows, or from the old tail when negative)
 __global__ void conv_tail_kernel(const float* __restrict__ h, float* __restrict__ tail, const int* __restrict__ cu,
                                  const int* __restrict__ slot, int C, int taps) {
@@ -109,6 +146,57 @@ __global__ void conv_tail_kernel(const float* __restrict__ h, float* __restrict_
 }
 
 // ------------------------------------------------------------------------------------------------ norms
+// C % 4 == 0: 16-byte loads, the row of y stays in registers between the two passes (up to 4 vectors per thread).
+template <typename T>
+__global__ void add_rmsnorm4_kernel(const float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ w,
+                                    float* __restrict__ x_out, T* __restrict__ x_act, int C, float eps) {
+    __shared__ float red[32];
+    const long long row = blockIdx.x;
+    const float4* yr = reinterpret_cast<const float4*>(y + row * C);
+    const int nv = C >> 2;
+    float4 keep[4];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int v = threadIdx.x + i * blockDim.x;
+        if (v < nv) {
+            keep[i] = yr[v];
+            ss += keep[i].x * keep[i].x + keep[i].y * keep[i].y + keep[i].z * keep[i].z + keep[i].w * keep[i].w;
+        }
+    }
+    for (int v = threadIdx.x + 4 * blockDim.x; v < nv; v += blockDim.x) {
+        const float4 a = yr[v];
+        ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+    }
+    ss = block_sum(ss, red);
+    const float r = 1.0f / sqrtf(ss / (float)C + eps);
+    const float4* xr = reinterpret_cast<const float4*>(x + row * C);
+    const float4* wr = reinterpret_cast<const float4*>(w);
+    float4* outr = reinterpret_cast<float4*>(x_out + row * C);
+    auto emit = [&](int v, const float4& a) {
+        const float4 xv = xr[v], wv = wr[v];
+        float4 o;
+        o.x = xv.x + a.x * r * wv.x;
+        o.y = xv.y + a.y * r * wv.y;
+        o.z = xv.z + a.z * r * wv.z;
+        o.w = xv.w + a.w * r * wv.w;
+        outr[v] = o;
+        if (x_act) {
+            T* xa = x_act + row * C + 4 * v;
+            stf(xa, o.x);
+            stf(xa + 1, o.y);
+            stf(xa + 2, o.z);
+            stf(xa + 3, o.w);
+        }
+    };
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int v = threadIdx.x + i * blockDim.x;
+        if (v < nv) emit(v, keep[i]);
+    }
+    for (int v = threadIdx.x + 4 * blockDim.x; v < nv; v += blockDim.x) emit(v, yr[v]);
+}
+
 template <typename T>
 __global__ void add_rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ w,
                                    float* __restrict__ x_out, T* __restrict__ x_act, int C, float eps) {
@@ -266,7 +354,16 @@ extern "C" int llark_seq_short_conv(const float* h, const float* w, float* tail,
                                     cudaStream_t st) {
     if (n_tok <= 0 || C <= 0 || taps < 1 || !h || !w || !y || (taps > 1 && !tail)) return LLARK_EINVAL;
     const int th = norm_threads(C);
-    if (act_fp32)
+    const bool v4 = (C % 4 == 0) && (((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(tail)) & 15) == 0);
+    if (v4) {
+        int t4 = 32;
+        while (t4 * 4 < C && t4 < 256) t4 <<= 1;
+        if (act_fp32)
+            short_conv4_kernel<float><<<n_tok, t4, 0, st>>>(h, w, tail, tok_seq, cu, slot, (float*)y, C, taps, inline_tail);
+        else
+            short_conv4_kernel<bf16_t><<<n_tok, t4, 0, st>>>(h, w, tail, tok_seq, cu, slot, (bf16_t*)y, C, taps,
+                                                            inline_tail);
+    } else if (act_fp32)
         short_conv_kernel<float><<<n_tok, th, 0, st>>>(h, w, tail, tok_seq, cu, slot, (float*)y, C, taps, inline_tail);
     else
         short_conv_kernel<bf16_t><<<n_tok, th, 0, st>>>(h, w, tail, tok_seq, cu, slot, (bf16_t*)y, C, taps, inline_tail);
@@ -285,7 +382,16 @@ extern "C" int llark_seq_add_rmsnorm(const float* x, const float* y, const float
                                      long long rows, int C, float eps, int act_fp32, cudaStream_t st) {
     if (rows <= 0 || C <= 0 || !x || !y || !w || !x_out) return LLARK_EINVAL;
     const int th = norm_threads(C);
-    if (act_fp32)
+    const bool v4 = (C % 4 == 0) && (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) |
+                                       reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(x_out)) & 15) == 0);
+    if (v4) {
+        int t4 = 32;
+        while (t4 * 8 < C && t4 < 256) t4 <<= 1;  // two vectors per thread at the usual widths
+        if (act_fp32)
+            add_rmsnorm4_kernel<float><<<(unsigned)rows, t4, 0, st>>>(x, y, w, x_out, (float*)x_act, C, eps);
+        else
+            add_rmsnorm4_kernel<bf16_t><<<(unsigned)rows, t4, 0, st>>>(x, y, w, x_out, (bf16_t*)x_act, C, eps);
+    } else if (act_fp32)
         add_rmsnorm_kernel<float><<<(unsigned)rows, th, 0, st>>>(x, y, w, x_out, (float*)x_act, C, eps);
     else
         add_rmsnorm_kernel<bf16_t><<<(unsigned)rows, th, 0, st>>>(x, y, w, x_out, (bf16_t*)x_act, C, eps);

@@ -1,0 +1,235 @@
+// Sliding-window attention for prompts and portions of prompts on the packed-step layout (see seq_mixers.cu), bf16
+// operands on the warp-level tensor-core path (mma.sync m16n8k16, fp32 accumulation): scores, mask, softmax and the
+// running maximum / sum are fp32, the probabilities are rounded to bf16 only as the A operand of P.V.
+//
+// CTA = 4 warps = 64 queries of one (request, head); it walks the 64-key tiles that intersect the window of any of its
+// queries. A key at position j of the sequence comes from the step's own buffers when j >= pos0 (it arrived with this
+// step) and from ring entry j % cap of the request's slot otherwise. K tiles sit in shared memory row-major, V tiles
+// transposed ([channel][key]) so that both B operands are read as 32-bit words; the row pitch (+8 elements) makes every
+// fragment load conflict-free. Per-head score scale (softmax scale x temperature) and the optional sigmoid output gate
+// are applied in registers. The SIMT kernel of seq_mixers.cu remains the path for single-token steps, fp32 and head
+// sizes that are not multiples of 16.
+#include "common.cuh"
+
+namespace llark {
+extern thread_local int g_last_cuda_error;
+namespace swamma {
+
+typedef __nv_bfloat16 bf16_t;
+constexpr int BQ = 64, BK = 64;
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int DMAX>
+__global__ void __launch_bounds__(128)
+swa_mma_kernel(const bf16_t* __restrict__ qn, const bf16_t* __restrict__ kn, const bf16_t* __restrict__ vv,
+               const bf16_t* __restrict__ kring, const bf16_t* __restrict__ vring, const float* __restrict__ gate,
+               long long gate_ld, const float* __restrict__ scale_h, bf16_t* __restrict__ out,
+               const int* __restrict__ cu, const int* __restrict__ pos0, const int* __restrict__ slot, int H, int G,
+               int D, int window, int cap) {
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int g = h / (H / G);
+    const int row0 = cu[b], n = cu[b + 1] - row0;
+    const int qt0 = blockIdx.x * BQ;
+    if (qt0 >= n) return;
+    const long long p0 = pos0[b];
+    extern __shared__ __align__(16) unsigned char smraw[];
+    const int DS = D + 8, KS = BK + 8;
+    bf16_t* sQ = reinterpret_cast<bf16_t*>(smraw);  // [BQ][DS]
+    bf16_t* sK = sQ + BQ * DS;                      // [BK][DS]
+    bf16_t* sVt = sK + BK * DS;                     // [D][KS]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
+    const int dv = D >> 3;  // 16-byte vectors per row
+
+    for (int i = threadIdx.x; i < BQ * dv; i += blockDim.x) {
+        const int r = i / dv, c = (i % dv) * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (qt0 + r < n) v = *reinterpret_cast<const uint4*>(qn + ((long long)(row0 + qt0 + r) * H + h) * D + c);
+        *reinterpret_cast<uint4*>(sQ + r * DS + c) = v;
+    }
+    const int q_last = (qt0 + BQ - 1 < n - 1) ? qt0 + BQ - 1 : n - 1;
+    const long long pq_lo = p0 + qt0, pq_hi = p0 + q_last;
+    const long long k_lo = pq_lo - window + 1 > 0 ? pq_lo - window + 1 : 0;
+    const long long ring_base = (long long)slot[b] * cap;
+    const float sc = scale_h[h];
+
+    float o[DMAX / 8][4];
+#pragma unroll
+    for (int i = 0; i < DMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    const int qrow = warp * 16 + gq;  // this thread's rows: qrow and qrow + 8
+
+    for (long long kt = k_lo; kt <= pq_hi; kt += BK) {
+        __syncthreads();  // the previous tile's fragments have been read (and sQ is written on the first pass)
+        for (int i = threadIdx.x; i < BK * dv; i += blockDim.x) {
+            const int r = i / dv, c = (i % dv) * 8;
+            const long long j = kt + r;
+            uint4 kq = make_uint4(0, 0, 0, 0), vq = make_uint4(0, 0, 0, 0);
+            if (j <= pq_hi) {
+                const long long e = j >= p0 ? ((long long)(row0 + (j - p0)) * G + g) : ((ring_base + (j % cap)) * G + g);
+                const bf16_t* kp = (j >= p0 ? kn : kring) + e * D + c;
+                const bf16_t* vp = (j >= p0 ? vv : vring) + e * D + c;
+                kq = *reinterpret_cast<const uint4*>(kp);
+                vq = *reinterpret_cast<const uint4*>(vp);
+            }
+            *reinterpret_cast<uint4*>(sK + r * DS + c) = kq;
+            const bf16_t* ve = reinterpret_cast<const bf16_t*>(&vq);
+#pragma unroll
+            for (int x = 0; x < 8; ++x) sVt[(c + x) * KS + r] = ve[x];
+        }
+        __syncthreads();
+        // ---- S = Q K^T for this warp's 16 rows x 64 keys
+        float s[BK / 8][4];
+#pragma unroll
+        for (int nt = 0; nt < BK / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+        for (int kb = 0; kb < DMAX / 16; ++kb) {
+            if (kb * 16 < D) {
+                const bf16_t* qa = sQ + qrow * DS + kb * 16 + 2 * tq;
+                const uint32_t a0 = *reinterpret_cast<const uint32_t*>(qa);
+                const uint32_t a1 = *reinterpret_cast<const uint32_t*>(qa + 8 * DS);
+                const uint32_t a2 = *reinterpret_cast<const uint32_t*>(qa + 8);
+                const uint32_t a3 = *reinterpret_cast<const uint32_t*>(qa + 8 * DS + 8);
+#pragma unroll
+                for (int nt = 0; nt < BK / 8; ++nt) {
+                    const bf16_t* kb_ = sK + (nt * 8 + gq) * DS + kb * 16 + 2 * tq;
+                    mma_bf16(s[nt], a0, a1, a2, a3, *reinterpret_cast<const uint32_t*>(kb_),
+                             *reinterpret_cast<const uint32_t*>(kb_ + 8));
+                }
+            }
+        }
+        // ---- scale, mask (causal and window), online softmax in fp32
+        float mt[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < BK / 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int r = qrow + (e >> 1) * 8;
+                const long long qp = p0 + qt0 + r, kp = kt + nt * 8 + 2 * tq + (e & 1);
+                const bool ok = (qt0 + r < n) && kp <= qp && qp - kp < window;
+                s[nt][e] = ok ? s[nt][e] * sc : -INFINITY;
+                mt[e >> 1] = fmaxf(mt[e >> 1], s[nt][e]);
+            }
+        float alpha[2], mn[2];
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+            mt[x] = fmaxf(mt[x], __shfl_xor_sync(0xffffffffu, mt[x], 1));
+            mt[x] = fmaxf(mt[x], __shfl_xor_sync(0xffffffffu, mt[x], 2));
+            mn[x] = fmaxf(m[x], mt[x]);
+            alpha[x] = mn[x] == -INFINITY ? 1.f : expf(m[x] - mn[x]);
+            m[x] = mn[x];
+            l[x] *= alpha[x];
+        }
+#pragma unroll
+        for (int nt = 0; nt < BK / 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int x = e >> 1;
+                const float p = mn[x] == -INFINITY ? 0.f : expf(s[nt][e] - mn[x]);
+                s[nt][e] = p;
+                l[x] += p;
+            }
+#pragma unroll
+        for (int i = 0; i < DMAX / 8; ++i) {
+            o[i][0] *= alpha[0];
+            o[i][1] *= alpha[0];
+            o[i][2] *= alpha[1];
+            o[i][3] *= alpha[1];
+        }
+        // ---- O += P V
+#pragma unroll
+        for (int kb = 0; kb < BK / 16; ++kb) {
+            const uint32_t a0 = pack_bf16x2(s[2 * kb][0], s[2 * kb][1]);
+            const uint32_t a1 = pack_bf16x2(s[2 * kb][2], s[2 * kb][3]);
+            const uint32_t a2 = pack_bf16x2(s[2 * kb + 1][0], s[2 * kb + 1][1]);
+            const uint32_t a3 = pack_bf16x2(s[2 * kb + 1][2], s[2 * kb + 1][3]);
+#pragma unroll
+            for (int nt = 0; nt < DMAX / 8; ++nt) {
+                if (nt * 8 < D) {
+                    const bf16_t* vb = sVt + (nt * 8 + gq) * KS + kb * 16 + 2 * tq;
+                    mma_bf16(o[nt], a0, a1, a2, a3, *reinterpret_cast<const uint32_t*>(vb),
+                             *reinterpret_cast<const uint32_t*>(vb + 8));
+                }
+            }
+        }
+    }
+    // ---- normalise, gate, store
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        l[x] += __shfl_xor_sync(0xffffffffu, l[x], 1);
+        l[x] += __shfl_xor_sync(0xffffffffu, l[x], 2);
+    }
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        const int r = qrow + x * 8;
+        if (qt0 + r >= n) continue;
+        const long long trow = row0 + qt0 + r;
+        const float inv = 1.0f / l[x];
+#pragma unroll
+        for (int nt = 0; nt < DMAX / 8; ++nt) {
+            if (nt * 8 < D) {
+                const int c = nt * 8 + 2 * tq;
+                float v0 = o[nt][2 * x] * inv, v1 = o[nt][2 * x + 1] * inv;
+                if (gate) {
+                    const float* gp = gate + trow * gate_ld + h * D + c;
+                    v0 *= 1.0f / (1.0f + expf(-gp[0]));
+                    v1 *= 1.0f / (1.0f + expf(-gp[1]));
+                }
+                *reinterpret_cast<uint32_t*>(out + (trow * H + h) * D + c) = pack_bf16x2(v0, v1);
+            }
+        }
+    }
+}
+
+template <int DMAX>
+static int launch(const void* qn, const void* kn, const void* vv, const void* kring, const void* vring,
+                  const float* gate, long long gate_ld, const float* scale_h, void* out, const int* cu, const int* pos0,
+                  const int* slot, int n_seq, int max_len, int H, int G, int D, int window, int cap, cudaStream_t st) {
+    const size_t smem = sizeof(bf16_t) * ((size_t)(BQ + BK) * (D + 8) + (size_t)D * (BK + 8));
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(swa_mma_kernel<DMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            g_last_cuda_error = (int)e;
+            return LLARK_ECUDA;
+        }
+    }
+    dim3 grid((max_len + BQ - 1) / BQ, H, n_seq);
+    swa_mma_kernel<DMAX><<<grid, 128, smem, st>>>((const bf16_t*)qn, (const bf16_t*)kn, (const bf16_t*)vv,
+                                                  (const bf16_t*)kring, (const bf16_t*)vring, gate, gate_ld, scale_h,
+                                                  (bf16_t*)out, cu, pos0, slot, H, G, D, window, cap);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        g_last_cuda_error = (int)e;
+        return LLARK_ECUDA;
+    }
+    return LLARK_OK;
+}
+
+}  // namespace swamma
+}  // namespace llark
+
+using namespace llark;
+
+extern "C" int llark_seq_swa_attn_mma(const void* qn, const void* kn, const void* vv, const void* kring, const void* vring,
+                                      const float* gate, long long gate_ld, const float* scale_h, void* out,
+                                      const int* cu, const int* pos0, const int* slot, int n_seq, int max_len, int H,
+                                      int G, int D, int window, int cap, cudaStream_t st) {
+    if (n_seq <= 0 || max_len <= 0 || H <= 0 || G <= 0 || (H % G) || D <= 0 || (D % 16) || D > 256 || window <= 0 ||
+        cap <= 0 || !qn || !kn || !vv || !kring || !vring || !scale_h || !out || !cu || !pos0 || !slot)
+        return LLARK_EINVAL;
+    if (gate && (gate_ld % 2)) return LLARK_EINVAL;
+    if (D <= 64)
+        return swamma::launch<64>(qn, kn, vv, kring, vring, gate, gate_ld, scale_h, out, cu, pos0, slot, n_seq, max_len, H,
+                                  G, D, window, cap, st);
+    if (D <= 128)
+        return swamma::launch<128>(qn, kn, vv, kring, vring, gate, gate_ld, scale_h, out, cu, pos0, slot, n_seq, max_len,
+                                   H, G, D, window, cap, st);
+    return swamma::launch<256>(qn, kn, vv, kring, vring, gate, gate_ld, scale_h, out, cu, pos0, slot, n_seq, max_len, H, G,
+                               D, window, cap, st);
+}

@@ -580,8 +580,18 @@ def seq_qk_headnorm(src, q_off, k_off, wq, wk, H, G, D, eps, act, st=None, kring
     return qn, kn, vr
 
 
+SWA_MMA_MIN_LEN = 16  # shortest longest-request of a step that goes to the tensor-core attention kernel
+
+
 def seq_swa_attn(qn, kn, vv, kring, vring, gate, gate_ld, scale_h, st, H, G, D, E, window, cap, from_ring_only):
     out = torch.empty((st.n_tok, H * E), device=qn.device, dtype=qn.dtype)
+    if (qn.dtype == BF16 and not from_ring_only and st.max_len >= SWA_MMA_MIN_LEN and D == E and D % 16 == 0
+            and D <= 256 and gate_ld % 2 == 0):
+        # prompts and portions: 64-query tiles on the tensor cores; single tokens, fp32 and odd head sizes stay SIMT
+        check(lib().llark_seq_swa_attn_mma(_p(qn), _p(kn), _p(vv), _p(kring), _p(vring), _p(gate), gate_ld, _p(scale_h),
+                                           _p(out), _p(st.cu), _p(st.pos0), _p(st.slot), st.n_seq, st.max_len, H, G, D,
+                                           window, cap, _stream()), "seq_swa_attn_mma")
+        return out
     check(lib().llark_seq_swa_attn(_p(qn), _p(kn), _p(vv), _p(kring), _p(vring), _p(gate), gate_ld, _p(scale_h), _p(out),
                                    _p(st.tok_seq), _p(st.cu), _p(st.pos0), _p(st.slot), st.n_tok, H, G, D, E, window, cap,
                                    int(from_ring_only), _actf(qn.dtype), _stream()), "seq_swa_attn")
@@ -594,12 +604,33 @@ def seq_kv_ring_write(kn, vv, kring, vring, st, cap):
           "seq_kv_ring_write")
 
 
+GLR_CHUNK = 128        # rows per work item when a long prompt is scanned in chunks
+GLR_CHUNK_MIN_LEN = 512  # shortest longest-request of a step that is scanned in chunks
+
+
 def seq_glr_scan(src, q_off, f_off, v_off, lower, state, st, H, D, E):
-    """src fp32 [n_tok, ld] -> o_raw fp32 [n_tok, H*E]; state fp32 [slots, H, D, E] read and written back."""
+    """src fp32 [n_tok, ld] -> o_raw fp32 [n_tok, H*E]; state fp32 [slots, H, D, E] read and written back. Steps with a
+    long request run in three passes over chunks of GLR_CHUNK rows (local states from zero; combine; outputs), which
+    gives the scan as many independent work items as there are chunks."""
     _req(src, torch.float32), _req(state, torch.float32)
     o = torch.empty((st.n_tok, H * E), device=src.device, dtype=torch.float32)
-    check(lib().llark_seq_glr_scan(_p(src), src.stride(0), q_off, f_off, v_off, _p(lower), _p(state), _p(o), _p(st.cu),
-                                   _p(st.slot), st.n_seq, H, D, E, _stream()), "seq_glr_scan")
+    L = lib()
+    if st.max_len < GLR_CHUNK_MIN_LEN:
+        check(L.llark_seq_glr_scan(_p(src), src.stride(0), q_off, f_off, v_off, _p(lower), _p(state), _p(state), None,
+                                   _p(o), _p(st.cu), _p(st.lens_dev), _p(st.slot), _p(st.slot), st.n_seq, H, D, E,
+                                   _stream()), "seq_glr_scan")
+        return o
+    ch = st.chunks(GLR_CHUNK)
+    cstate = torch.empty((ch.n_items, H, D, E), device=src.device, dtype=torch.float32)
+    cdecay = torch.empty((ch.n_items, H, D), device=src.device, dtype=torch.float32)
+    check(L.llark_seq_glr_scan(_p(src), src.stride(0), q_off, f_off, v_off, _p(lower), None, _p(cstate), _p(cdecay), None,
+                               _p(ch.row0), _p(ch.n), _p(ch.minus1), _p(ch.index), ch.n_items, H, D, E, _stream()),
+          "seq_glr_scan(local)")
+    check(L.llark_seq_glr_combine(_p(state), _p(cstate), _p(cdecay), _p(ch.seq_item0), _p(st.slot), st.n_seq, H, D, E,
+                                  _stream()), "seq_glr_combine")
+    check(L.llark_seq_glr_scan(_p(src), src.stride(0), q_off, f_off, v_off, _p(lower), _p(cstate), _p(state), None, _p(o),
+                               _p(ch.row0), _p(ch.n), _p(ch.index), _p(ch.last_slot), ch.n_items, H, D, E, _stream()),
+          "seq_glr_scan(outputs)")
     return o
 
 

@@ -23,7 +23,7 @@ class StepLayout:
         n_tok = int(sum(lens))
         if n_seq == 0 or min(lens) <= 0:
             raise ValueError("a step needs at least one token for every request in it")
-        host = torch.empty(n_tok + 3 * n_seq + 1, dtype=torch.int32, pin_memory=torch.device(device).type == "cuda")
+        host = torch.empty(n_tok + 4 * n_seq + 1, dtype=torch.int32, pin_memory=torch.device(device).type == "cuda")
         cu = [0]
         for n in lens:
             cu.append(cu[-1] + int(n))
@@ -33,16 +33,53 @@ class StepLayout:
         host[:n_tok] = torch.tensor(seq, dtype=torch.int32)
         host[n_tok:n_tok + n_seq + 1] = torch.tensor(cu, dtype=torch.int32)
         host[n_tok + n_seq + 1:n_tok + 2 * n_seq + 1] = torch.tensor([int(p) for p in pos0], dtype=torch.int32)
-        host[n_tok + 2 * n_seq + 1:] = torch.tensor([int(s) for s in slots], dtype=torch.int32)
+        host[n_tok + 2 * n_seq + 1:n_tok + 3 * n_seq + 1] = torch.tensor([int(s) for s in slots], dtype=torch.int32)
+        host[n_tok + 3 * n_seq + 1:] = torch.tensor([int(n) for n in lens], dtype=torch.int32)
         dev = host.to(device, non_blocking=True)
         self._host = host  # keeps the pinned buffer alive until the copy has run
         self.tok_seq = dev[:n_tok]
         self.cu = dev[n_tok:n_tok + n_seq + 1]
         self.pos0 = dev[n_tok + n_seq + 1:n_tok + 2 * n_seq + 1]
-        self.slot = dev[n_tok + 2 * n_seq + 1:]
+        self.slot = dev[n_tok + 2 * n_seq + 1:n_tok + 3 * n_seq + 1]
+        self.lens_dev = dev[n_tok + 3 * n_seq + 1:]
+        self.device, self.slots_host, self._chunks = device, [int(s) for s in slots], {}
         self.n_tok, self.n_seq = n_tok, n_seq
         self.max_len = int(max(lens))
         self.lens, self.cu_host, self.pos0_host = [int(n) for n in lens], cu, [int(p) for p in pos0]
+
+
+class _Chunks:
+    pass
+
+
+def _step_chunks(self, length):
+    """The step cut into work items of at most `length` consecutive rows of one request (for scans that run long
+    prompts as independent chunks): row0 / n per item, index = 0 .. n_items-1, minus1 = -1 everywhere, last_slot = the
+    request's slot on its last item and -1 elsewhere, seq_item0[b] = first item of request b. Built once per step."""
+    if length in self._chunks:
+        return self._chunks[length]
+    row0, n, last, seq0 = [], [], [], [0]
+    for b, ln in enumerate(self.lens):
+        for lo in range(0, ln, length):
+            row0.append(self.cu_host[b] + lo)
+            n.append(min(length, ln - lo))
+            last.append(self.slots_host[b] if lo + length >= ln else -1)
+        seq0.append(len(row0))
+    k = len(row0)
+    host = torch.tensor(row0 + n + list(range(k)) + [-1] * k + last + seq0, dtype=torch.int32)
+    if torch.device(self.device).type == "cuda":
+        host = host.pin_memory()
+    dev = host.to(self.device, non_blocking=True)
+    c = _Chunks()
+    c._host = host
+    c.n_items = k
+    c.row0, c.n, c.index, c.minus1, c.last_slot = (dev[i * k:(i + 1) * k] for i in range(5))
+    c.seq_item0 = dev[5 * k:]
+    self._chunks[length] = c
+    return c
+
+
+StepLayout.chunks = _step_chunks
 
 
 class StateCache:

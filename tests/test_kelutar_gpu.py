@@ -68,6 +68,9 @@ CONFIGS = {
     # attention first, window 1 (sees itself only) and a wide one, no convolution (1 tap), ff on the recurrence
     "attn_first": _cfg([_at(2, 1, 40, 1), _hg(1, 36, 8, mlp={"kind": "dense", "ff": 64}), _at(6, 6, 16, 9)],
                        vocab=64, width=48, taps=1, scale=1.0, eps=1e-3),
+    # head sizes the tensor-core attention takes (multiples of 16), a window wider than one key tile, three taps
+    "tc_heads": _cfg([_at(4, 2, 32, 70, mlp=FF), _hg(2, 32, 48), _at(4, 2, 32, 70, mlp=FF, weights_of=0),
+                      _at(2, 2, 64, 3)], vocab=120, width=64, taps=3),
     # two taps, one head, head sizes above 32 and 128
     "wide_heads": _cfg([_hg(2, 144, 40), _at(1, 1, 72, 5, scale=0.2, mlp=FF)], vocab=50, width=80, taps=2),
 }
@@ -190,6 +193,30 @@ def test_window_attention_sees_exactly_its_window(window):
     assert _rel(bf, ko.sliding_softmax_attention(q16, k16, v16, window, scale_h.double())) < 1e-2
 
 
+@pytest.mark.parametrize("D,window", [(16, 1), (48, 5), (32, 64), (64, 65), (128, 100), (80, 31), (192, 70)])
+def test_window_attention_on_the_tensor_core_path(D, window):
+    """Prompts and portions of 16 tokens or more take the 64-query tensor-core kernel: same needles at the window's edge,
+    tiles that start before position 0, queries whose window misses a whole key tile, keys from the ring and from the
+    step, grouped key heads."""
+    T, H, G = 230, 4, 2
+    g = torch.Generator().manual_seed(D + window)
+    q = torch.randn(T, H, D, generator=g) * 0.1
+    k = torch.randn(T, G, D, generator=g) * 0.1
+    v = torch.randn(T, G, D, generator=g)
+    for i in range(T):
+        j = i - (window - 1) if i % 2 == 0 else i - window
+        if j >= 0:
+            u = torch.nn.functional.normalize(torch.randn(D, generator=g), dim=0)
+            q[i] += 5.0 * u
+            k[j] += 5.0 * u
+    scale_h = torch.tensor([1.0, 0.7, 1.3, 0.5])
+    q16, k16, v16 = (t.to(BF16).double() for t in (q, k, v))
+    want = ko.sliding_softmax_attention(q16, k16, v16, window, scale_h.double())
+    for portions in ([T], [130, 40, 17, 1, 1, 41], [16, 16, 64, 70, 64]):
+        got = _run_window_attention(q, k, v, window, scale_h, portions, BF16)
+        assert _rel(got, want) < 1e-2, portions
+
+
 def test_qk_headnorm_and_gate_through_the_mixer():
     from llark_b200.mixers import GatedWindowAttention
     from llark_b200.state_cache import StateCache
@@ -212,13 +239,17 @@ def test_qk_headnorm_and_gate_through_the_mixer():
         assert _rel(torch.cat(outs), want) < tol
 
 
+@pytest.mark.parametrize("chunked", [False, True])
 @pytest.mark.parametrize("H,D,E", [(3, 20, 24), (1, 144, 40), (2, 16, 130), (5, 48, 64)])
-def test_gated_recurrence_remembers_far_tokens(H, D, E):
+def test_gated_recurrence_remembers_far_tokens(H, D, E, chunked, monkeypatch):
     """Every seventh channel forgets almost nothing (gate ~ 1) except at step 3, where its gate opens and a large value
     is written; 300 steps later that value still carries the output, so a lost or re-zeroed state shows. The steps are
     cut into a prompt, portions and single tokens; a second request shares the batch and ends early."""
     from llark_b200 import ops
 
+    if chunked:  # the three-pass form: chunks of 16 rows (the last one partial) for every portion of 32 rows or more
+        monkeypatch.setattr(ops, "GLR_CHUNK", 16)
+        monkeypatch.setattr(ops, "GLR_CHUNK_MIN_LEN", 32)
     T = 330
     g = torch.Generator().manual_seed(H * D + E)
     ld = 2 * H * D + H * E + 3  # a padded row, as a fused projection may have
