@@ -194,7 +194,7 @@ __global__ void kv_ring_write_kernel(const T* __restrict__ kn, const T* __restri
 // registers; R threads (adjacent lanes) share a column and add their partial outputs by shuffle. The inputs of TS steps
 // are brought to shared memory with cp.async while the previous TS steps are computed, and the gate arithmetic is done
 // once per element there.
-constexpr int kTS = 16;
+constexpr int kTS = 8;  // steps per stage: two stages of a 128-wide head stay under 32 KB, six CTAs per SM
 
 __device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
@@ -206,7 +206,7 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 // slot of the state store), or one chunk of a long prompt (three passes, see llark_seq_glr_scan). item_init / item_final
 // index init_buf / final_buf ([*, H, D, E]); -1 = start from zero / keep nothing. decay_buf (optional) [items, H, D]
 // receives the product of the item's forget gates per channel; o_raw may be NULL (no outputs wanted).
-template <int DPT>
+template <int DPT, int EC, bool OUT>
 __global__ void glr_scan_kernel(const float* __restrict__ src, long long ld, int q_off, int f_off, int v_off,
                                 const float* __restrict__ lower, const float* __restrict__ init_buf,
                                 float* __restrict__ final_buf, float* __restrict__ decay_buf, float* __restrict__ o_raw,
@@ -219,15 +219,16 @@ __global__ void glr_scan_kernel(const float* __restrict__ src, long long ld, int
     const int stage_floats = kTS * (3 * DP + ecols);
     const int h = blockIdx.y, b = blockIdx.z;
     const int r = threadIdx.x % R, ec = threadIdx.x / R;
-    const int e = blockIdx.x * ecols + ec;
+    const int e0 = blockIdx.x * ecols + ec * EC;  // this thread's EC adjacent columns: a DPT x EC tile of S in registers
     const int row0 = item_row0[b], n = item_n[b];
     const int i_init = item_init[b], i_final = item_final[b];
     const float* st_in = i_init >= 0 ? init_buf + ((long long)i_init * H + h) * (long long)D * E : nullptr;
-    float S[DPT];
+    float S[DPT][EC];
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
         const int d = r * DPT + i;
-        S[i] = (st_in && d < D && e < E) ? st_in[(long long)d * E + e] : 0.f;
+#pragma unroll
+        for (int c = 0; c < EC; ++c) S[i][c] = (st_in && d < D && e0 + c < E) ? st_in[(long long)d * E + e0 + c] : 0.f;
     }
     const bool want_decay = decay_buf != nullptr && blockIdx.x == 0;
     float decay[8];  // rows threadIdx.x + k * blockDim.x (8 * 32 >= the widest padded head)
@@ -285,18 +286,32 @@ __global__ void glr_scan_kernel(const float* __restrict__ src, long long ld, int
             }
         }
         for (int ts = 0; ts < steps; ++ts) {
-            const float vt = e < E ? buf[3 * kTS * DP + ts * ecols + ec] : 0.f;
+            float vt[EC], part[EC];
+#pragma unroll
+            for (int c = 0; c < EC; ++c) {
+                vt[c] = e0 + c < E ? buf[3 * kTS * DP + ts * ecols + ec * EC + c] : 0.f;
+                part[c] = 0.f;
+            }
             const float* q = buf + ts * DP + r * DPS;
             const float* f = q + kTS * DP;
             const float* g = f + kTS * DP;
-            float part = 0.f;
 #pragma unroll
             for (int i = 0; i < DPT; ++i) {
-                S[i] = fmaf(f[i], S[i], g[i] * vt);
-                part = fmaf(S[i], q[i], part);
+                const float fi = f[i], gi = g[i], qi = q[i];  // read once, used for all EC columns
+#pragma unroll
+                for (int c = 0; c < EC; ++c) {
+                    S[i][c] = fmaf(fi, S[i][c], gi * vt[c]);
+                    if (OUT) part[c] = fmaf(S[i][c], qi, part[c]);
+                }
             }
-            for (int o = R >> 1; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-            if (o_raw && r == 0 && e < E) o_raw[(long long)(row0 + s * kTS + ts) * ((long long)H * E) + h * E + e] = part;
+            if (OUT) {
+#pragma unroll
+                for (int c = 0; c < EC; ++c) {
+                    for (int o = R >> 1; o > 0; o >>= 1) part[c] += __shfl_xor_sync(0xffffffffu, part[c], o);
+                    if (r == 0 && e0 + c < E)
+                        o_raw[(long long)(row0 + s * kTS + ts) * ((long long)H * E) + h * E + e0 + c] = part[c];
+                }
+            }
         }
     }
     if (i_final >= 0) {
@@ -304,7 +319,9 @@ __global__ void glr_scan_kernel(const float* __restrict__ src, long long ld, int
 #pragma unroll
         for (int i = 0; i < DPT; ++i) {
             const int d = r * DPT + i;
-            if (d < D && e < E) st_out[(long long)d * E + e] = S[i];
+#pragma unroll
+            for (int c = 0; c < EC; ++c)
+                if (d < D && e0 + c < E) st_out[(long long)d * E + e0 + c] = S[i][c];
         }
     }
     if (want_decay) {
@@ -438,28 +455,38 @@ extern "C" int llark_seq_glr_scan(const float* src, long long ld, int q_off, int
     const int dpt = D <= 128 ? 16 : 32;
     int R = 1;
     while (R * dpt < D) R <<= 1;  // 1, 2, 4 or 8 row groups: a power of two for the shuffle tree
+    // each thread keeps a dpt x EC tile of S: the gates and q of a row are read from shared memory once per EC columns,
+    // which is what keeps the scan off the shared-memory bandwidth limit; narrow heads take fewer columns per thread
+    const int ec = (dpt == 16 && E >= 64) ? 4 : (E >= 32 ? 2 : 1);
     int threads = 128;
-    int ecols = threads / R;
-    while (ecols / 2 >= E && threads > 32) {  // narrow heads: do not carry idle columns
+    int ecols = threads / R * ec;
+    while (ecols / 2 >= E && threads > 32) {  // do not carry idle columns
         threads >>= 1;
         ecols >>= 1;
     }
     const int DP = R * (dpt + 1);
     const size_t smem = sizeof(float) * 2 * (size_t)kTS * (3 * DP + ecols);
     dim3 grid((E + ecols - 1) / ecols, H, n_items);
-    if (dpt == 16) {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(glr_scan_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        glr_scan_kernel<16><<<grid, threads, smem, st>>>(src, ld, q_off, f_off, v_off, lower, init_buf, final_buf,
-                                                         decay_buf, o_raw, item_row0, item_n, item_init, item_final, H, D,
-                                                         E, R, ecols);
-    } else {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(glr_scan_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        glr_scan_kernel<32><<<grid, threads, smem, st>>>(src, ld, q_off, f_off, v_off, lower, init_buf, final_buf,
-                                                         decay_buf, o_raw, item_row0, item_n, item_init, item_final, H, D,
-                                                         E, R, ecols);
-    }
+#define LLARK_GLR2(DPT_, EC_, OUT_)                                                                                        \
+    do {                                                                                                                   \
+        if (smem > 48 * 1024)                                                                                              \
+            cudaFuncSetAttribute(glr_scan_kernel<DPT_, EC_, OUT_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        glr_scan_kernel<DPT_, EC_, OUT_><<<grid, threads, smem, st>>>(src, ld, q_off, f_off, v_off, lower, init_buf,        \
+                                                                      final_buf, decay_buf, o_raw, item_row0, item_n,       \
+                                                                      item_init, item_final, H, D, E, R, ecols);            \
+    } while (0)
+#define LLARK_GLR(DPT_, EC_)                   \
+    do {                                       \
+        if (o_raw) LLARK_GLR2(DPT_, EC_, true); \
+        else LLARK_GLR2(DPT_, EC_, false);     \
+    } while (0)
+    if (dpt == 16 && ec == 4) LLARK_GLR(16, 4);
+    else if (dpt == 16 && ec == 2) LLARK_GLR(16, 2);
+    else if (dpt == 16) LLARK_GLR(16, 1);
+    else if (ec == 2) LLARK_GLR(32, 2);
+    else LLARK_GLR(32, 1);
+#undef LLARK_GLR2
+#undef LLARK_GLR
     return check_launch();
 }
 

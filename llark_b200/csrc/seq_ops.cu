@@ -132,6 +132,68 @@ __global__ void short_conv4_kernel(const float* __restrict__ h, const float* __r
     }
 }
 
+// Prompts: a CTA walks TB consecutive rows with the last TAPS-1 inputs of each 4-channel group in registers, so a row of
+// h and the taps are read once per CTA instead of once per output row (the per-row kernels above are bound by the number
+// of L1 requests, not by bytes). The window is rebuilt from h / the tail wherever a request starts inside the group.
+template <typename T> __device__ __forceinline__ void st4(T* p, float4 v);
+template <> __device__ __forceinline__ void st4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void st4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+    *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+}
+
+template <typename T, int TAPS, int TB>
+__global__ void short_conv4t_kernel(const float* __restrict__ h, const float* __restrict__ w,
+                                    const float* __restrict__ tail, const int* __restrict__ tok_seq,
+                                    const int* __restrict__ cu, const int* __restrict__ slot, T* __restrict__ y, int C,
+                                    int n_tok) {
+    const int t0 = blockIdx.x * TB;
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+    if (c >= C) return;
+    float wr[4][TAPS];
+#pragma unroll
+    for (int ch = 0; ch < 4; ++ch)
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) wr[ch][j] = w[(long long)(c + ch) * TAPS + j];
+    float4 win[TAPS > 1 ? TAPS - 1 : 1];
+    for (int i = 0; i < TB && t0 + i < n_tok; ++i) {
+        const int t = t0 + i;
+        const int b = tok_seq[t];
+        const int local = t - cu[b];
+        if (i == 0 || local < TAPS - 1) {
+            const float* tl = tail + (long long)slot[b] * (TAPS - 1) * C;
+#pragma unroll
+            for (int j = 0; j < TAPS - 1; ++j) {
+                const int s = local - (TAPS - 1) + j;
+                win[j] = *reinterpret_cast<const float4*>(s >= 0 ? h + (long long)(t - local + s) * C + c
+                                                                 : tl + (long long)(TAPS - 1 + s) * C + c);
+            }
+        }
+        const float4 cur = *reinterpret_cast<const float4*>(h + (long long)t * C + c);
+        float4 acc = make_float4(wr[0][TAPS - 1] * cur.x, wr[1][TAPS - 1] * cur.y, wr[2][TAPS - 1] * cur.z,
+                                 wr[3][TAPS - 1] * cur.w);
+#pragma unroll
+        for (int j = 0; j < TAPS - 1; ++j) {
+            acc.x = fmaf(wr[0][j], win[j].x, acc.x);
+            acc.y = fmaf(wr[1][j], win[j].y, acc.y);
+            acc.z = fmaf(wr[2][j], win[j].z, acc.z);
+            acc.w = fmaf(wr[3][j], win[j].w, acc.w);
+        }
+        st4(y + (long long)t * C + c, make_float4(cur.x + acc.x, cur.y + acc.y, cur.z + acc.z, cur.w + acc.w));
+#pragma unroll
+        for (int j = 0; j + 1 < TAPS - 1; ++j) win[j] = win[j + 1];
+        if (TAPS > 1) win[TAPS - 2] = cur;
+    }
+}
+
+template <typename T, int TAPS>
+static void launch_conv4t(const float* h, const float* w, const float* tail, const int* tok_seq, const int* cu,
+                          const int* slot, void* y, int n_tok, int C, cudaStream_t st) {
+    constexpr int TB = 16;
+    const int th = C / 4 < 128 ? ((C / 4 + 31) / 32) * 32 : 128;
+    dim3 grid((n_tok + TB - 1) / TB, (C / 4 + th - 1) / th);
+    short_conv4t_kernel<T, TAPS, TB><<<grid, th, 0, st>>>(h, w, tail, tok_seq, cu, slot, (T*)y, C, n_tok);
+}
+
 // new tail[k] = input at local index n - (taps-1) + k (from this step's rows, or from the old tail when negative)
 __global__ void conv_tail_kernel(const float* __restrict__ h, float* __restrict__ tail, const int* __restrict__ cu,
                                  const int* __restrict__ slot, int C, int taps) {
@@ -355,7 +417,17 @@ extern "C" int llark_seq_short_conv(const float* h, const float* w, float* tail,
     if (n_tok <= 0 || C <= 0 || taps < 1 || !h || !w || !y || (taps > 1 && !tail)) return LLARK_EINVAL;
     const int th = norm_threads(C);
     const bool v4 = (C % 4 == 0) && (((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(tail)) & 15) == 0);
-    if (v4) {
+    if (v4 && !inline_tail && taps >= 2 && taps <= 4 && n_tok >= 64) {
+        if (act_fp32) {
+            if (taps == 2) launch_conv4t<float, 2>(h, w, tail, tok_seq, cu, slot, y, n_tok, C, st);
+            else if (taps == 3) launch_conv4t<float, 3>(h, w, tail, tok_seq, cu, slot, y, n_tok, C, st);
+            else launch_conv4t<float, 4>(h, w, tail, tok_seq, cu, slot, y, n_tok, C, st);
+        } else {
+            if (taps == 2) launch_conv4t<bf16_t, 2>(h, w, tail, tok_seq, cu, slot, y, n_tok, C, st);
+            else if (taps == 3) launch_conv4t<bf16_t, 3>(h, w, tail, tok_seq, cu, slot, y, n_tok, C, st);
+            else launch_conv4t<bf16_t, 4>(h, w, tail, tok_seq, cu, slot, y, n_tok, C, st);
+        }
+    } else if (v4) {
         int t4 = 32;
         while (t4 * 4 < C && t4 < 256) t4 <<= 1;
         if (act_fp32)

@@ -4,10 +4,10 @@
 //
 // CTA = 4 warps = 64 queries of one (request, head); it walks the 64-key tiles that intersect the window of any of its
 // queries. A key at position j of the sequence comes from the step's own buffers when j >= pos0 (it arrived with this
-// step) and from ring entry j % cap of the request's slot otherwise. K tiles sit in shared memory row-major, V tiles
-// transposed ([channel][key]) so that both B operands are read as 32-bit words; the row pitch (+8 elements) makes every
-// fragment load conflict-free. Per-head score scale (softmax scale x temperature) and the optional sigmoid output gate
-// are applied in registers. The SIMT kernel of seq_mixers.cu remains the path for single-token steps, fp32 and head
+// step) and from ring entry j % cap of the request's slot otherwise. Q, K and V tiles sit in shared memory row-major and
+// reach the registers through ldmatrix (V through ldmatrix.trans); the row pitch (+8 elements) keeps those
+// conflict-free. Per-head score scale (softmax scale x temperature) and the optional sigmoid output gate are applied
+// in registers. The SIMT kernel of seq_mixers.cu remains the path for single-token steps, fp32 and head
 // sizes that are not multiples of 16.
 #include "common.cuh"
 
@@ -26,6 +26,17 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_u32(p)));
+}
+
 template <int DMAX>
 __global__ void __launch_bounds__(128)
 swa_mma_kernel(const bf16_t* __restrict__ qn, const bf16_t* __restrict__ kn, const bf16_t* __restrict__ vv,
@@ -40,10 +51,10 @@ swa_mma_kernel(const bf16_t* __restrict__ qn, const bf16_t* __restrict__ kn, con
     if (qt0 >= n) return;
     const long long p0 = pos0[b];
     extern __shared__ __align__(16) unsigned char smraw[];
-    const int DS = D + 8, KS = BK + 8;
-    bf16_t* sQ = reinterpret_cast<bf16_t*>(smraw);  // [BQ][DS]
+    const int DS = D + 8;                           // row pitch: 16 bytes more than the row, so that the eight
+    bf16_t* sQ = reinterpret_cast<bf16_t*>(smraw);  // [BQ][DS]   rows of an ldmatrix fall into different banks
     bf16_t* sK = sQ + BQ * DS;                      // [BK][DS]
-    bf16_t* sVt = sK + BK * DS;                     // [D][KS]
+    bf16_t* sV = sK + BK * DS;                      // [BK][DS]   row-major; P.V reads it through ldmatrix.trans
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
     const int dv = D >> 3;  // 16-byte vectors per row
 
@@ -79,9 +90,7 @@ swa_mma_kernel(const bf16_t* __restrict__ qn, const bf16_t* __restrict__ kn, con
                 vq = *reinterpret_cast<const uint4*>(vp);
             }
             *reinterpret_cast<uint4*>(sK + r * DS + c) = kq;
-            const bf16_t* ve = reinterpret_cast<const bf16_t*>(&vq);
-#pragma unroll
-            for (int x = 0; x < 8; ++x) sVt[(c + x) * KS + r] = ve[x];
+            *reinterpret_cast<uint4*>(sV + r * DS + c) = vq;
         }
         __syncthreads();
         // ---- S = Q K^T for this warp's 16 rows x 64 keys
@@ -91,16 +100,16 @@ swa_mma_kernel(const bf16_t* __restrict__ qn, const bf16_t* __restrict__ kn, con
 #pragma unroll
         for (int kb = 0; kb < DMAX / 16; ++kb) {
             if (kb * 16 < D) {
-                const bf16_t* qa = sQ + qrow * DS + kb * 16 + 2 * tq;
-                const uint32_t a0 = *reinterpret_cast<const uint32_t*>(qa);
-                const uint32_t a1 = *reinterpret_cast<const uint32_t*>(qa + 8 * DS);
-                const uint32_t a2 = *reinterpret_cast<const uint32_t*>(qa + 8);
-                const uint32_t a3 = *reinterpret_cast<const uint32_t*>(qa + 8 * DS + 8);
+                // A fragment: rows (lane & 7) + 8 * bit 3 of the warp's 16, columns + 8 for lanes 16..31
+                uint32_t a[4];
+                ldsm_x4(a, sQ + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * DS + kb * 16 + (lane >> 4) * 8);
 #pragma unroll
-                for (int nt = 0; nt < BK / 8; ++nt) {
-                    const bf16_t* kb_ = sK + (nt * 8 + gq) * DS + kb * 16 + 2 * tq;
-                    mma_bf16(s[nt], a0, a1, a2, a3, *reinterpret_cast<const uint32_t*>(kb_),
-                             *reinterpret_cast<const uint32_t*>(kb_ + 8));
+                for (int nt = 0; nt < BK / 8; nt += 2) {
+                    // B fragments of two key groups: (nt, k lo), (nt, k hi), (nt + 1, k lo), (nt + 1, k hi)
+                    uint32_t kf[4];
+                    ldsm_x4(kf, sK + ((nt + (lane >> 4)) * 8 + (lane & 7)) * DS + kb * 16 + ((lane >> 3) & 1) * 8);
+                    mma_bf16(s[nt], a[0], a[1], a[2], a[3], kf[0], kf[1]);
+                    mma_bf16(s[nt + 1], a[0], a[1], a[2], a[3], kf[2], kf[3]);
                 }
             }
         }
@@ -150,11 +159,13 @@ swa_mma_kernel(const bf16_t* __restrict__ qn, const bf16_t* __restrict__ kn, con
             const uint32_t a2 = pack_bf16x2(s[2 * kb + 1][0], s[2 * kb + 1][1]);
             const uint32_t a3 = pack_bf16x2(s[2 * kb + 1][2], s[2 * kb + 1][3]);
 #pragma unroll
-            for (int nt = 0; nt < DMAX / 8; ++nt) {
+            for (int nt = 0; nt < DMAX / 8; nt += 2) {
                 if (nt * 8 < D) {
-                    const bf16_t* vb = sVt + (nt * 8 + gq) * KS + kb * 16 + 2 * tq;
-                    mma_bf16(o[nt], a0, a1, a2, a3, *reinterpret_cast<const uint32_t*>(vb),
-                             *reinterpret_cast<const uint32_t*>(vb + 8));
+                    // transposed 8x8 blocks of V: (keys lo, nt), (keys hi, nt), (keys lo, nt + 1), (keys hi, nt + 1)
+                    uint32_t vf[4];
+                    ldsm_x4_trans(vf, sV + (kb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * DS + nt * 8 + (lane >> 4) * 8);
+                    mma_bf16(o[nt], a0, a1, a2, a3, vf[0], vf[1]);
+                    mma_bf16(o[nt + 1], a0, a1, a2, a3, vf[2], vf[3]);
                 }
             }
         }
@@ -191,7 +202,7 @@ template <int DMAX>
 static int launch(const void* qn, const void* kn, const void* vv, const void* kring, const void* vring,
                   const float* gate, long long gate_ld, const float* scale_h, void* out, const int* cu, const int* pos0,
                   const int* slot, int n_seq, int max_len, int H, int G, int D, int window, int cap, cudaStream_t st) {
-    const size_t smem = sizeof(bf16_t) * ((size_t)(BQ + BK) * (D + 8) + (size_t)D * (BK + 8));
+    const size_t smem = sizeof(bf16_t) * (size_t)(BQ + 2 * BK) * (D + 8);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(swa_mma_kernel<DMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) {

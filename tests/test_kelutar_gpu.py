@@ -114,13 +114,15 @@ def test_short_conv_carries_its_inputs_across_steps(taps):
     C = 40
     g = torch.Generator().manual_seed(taps)
     w = torch.randn(C, taps, generator=g)
-    seqs = [torch.randn(19, C, generator=g), torch.randn(11, C, generator=g)]
+    seqs = [torch.randn(19 + 150, C, generator=g), torch.randn(11 + 70, C, generator=g)]
     want = [ko.short_conv_residual(s.double(), w.double()) for s in seqs]
     tail = torch.full((6, max(taps - 1, 1), C), 7.0, device=_dev())  # other slots hold other requests' inputs
     tail[[4, 1]] = 0.0  # what alloc() does for the two slots in use
     slots = [4, 1]
     # request 0 in portions 5, 1, 1, 2, 10; request 1 in portions 2, 1, 8 (it ends earlier)
-    plan = [([5, 2], [0, 1]), ([1, 1], [0, 1]), ([1, 8], [0, 1]), ([2], [0]), ([10], [0])]
+    # ... then long portions (the row-blocked kernel: a request that starts in the middle of a block of rows)
+    plan = [([5, 2], [0, 1]), ([1, 1], [0, 1]), ([1, 8], [0, 1]), ([2], [0]), ([10], [0]), ([97, 3], [0, 1]),
+            ([53, 67], [0, 1])]
     at = [0, 0]
     got = [[], []]
     for lens, who in plan:
@@ -458,3 +460,62 @@ def test_checkpoint_folder_registry_and_greedy_generation(tmp_path):
     first_eos = want[1][9:].index(want[1][9 + 3])
     assert reqs[2].output == want[1][9:9 + first_eos + 1]
     assert all(r.finished for r in reqs) and not sched.cache.in_use()
+
+
+def test_command_line_and_trace_runner(tmp_path, monkeypatch, capsys):
+    """The two command-line entries on a checkpoint folder: generate_cli (scheduler, greedy) and the trace runner (given
+    tokens step by step: two requests start together with unequal prompts, decode together, one ends earlier, a third
+    starts later in the slot that was given back)."""
+    import io
+    import json
+
+    import numpy as np
+
+    from llark_b200 import generate_cli, trace_runner
+    from llark_b200.safetensors_io import save_file
+
+    cfg = CONFIGS["tc_heads"]
+    W = ko.random_weights(cfg, seed=9)
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    save_file({k: v.to(BF16) for k, v in W.items()}, str(tmp_path / "model.safetensors"))
+    V = cfg["vocab"]
+    a, b, c = _tokens(40, V, 1), _tokens(9, V, 2), _tokens(21, V, 3)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:30], "want": [0, 29]},
+                                     {"id": "b", "tokens": b[:5], "want": []}], "end": []}]
+    for k in range(4):
+        steps.append({"step": 1 + k, "entries": [{"id": "a", "tokens": [a[30 + k]], "want": [0]},
+                                                 {"id": "b", "tokens": [b[5 + k]], "want": [0]}],
+                      "end": ["b"] if k == 3 else []})
+    steps.append({"step": 5, "entries": [{"id": "c", "tokens": c, "want": [20]},
+                                         ], "end": ["c"]})
+    steps.append({"step": 6, "entries": [{"id": "a", "tokens": a[34:], "want": [5]}], "end": ["a"]})
+    out = tmp_path / "out"
+    monkeypatch.setattr("sys.stdin", io.StringIO("".join(json.dumps(s) + "\n" for s in steps)))
+    assert trace_runner.main(["--model", str(tmp_path), "--dtype", "float32", "--out", str(out), "--max-tokens", "80"]) == 0
+    printed = capsys.readouterr().out.split("\n")
+    assert [l for l in printed if l.startswith("done")] == ["done %d" % i for i in range(7)]
+    la, lb, lc = ko.forward(a, W, cfg), ko.forward(b, W, cfg), ko.forward(c, W, cfg)
+
+    def rows(i):
+        return torch.from_numpy(np.fromfile(out / ("%d.f32" % i), dtype="<f4").reshape(-1, V).copy())
+
+    assert _logit_err(rows(0), la[[0, 29]]) < 5e-5
+    for k in range(4):
+        assert _logit_err(rows(1 + k), torch.stack([la[30 + k], lb[5 + k]])) < 5e-5
+    assert _logit_err(rows(5), lc[[20]]) < 5e-5
+    assert _logit_err(rows(6), la[[39]]) < 5e-5
+
+    prompts = tmp_path / "p.jsonl"
+    prompts.write_text(json.dumps({"id": "x", "tokens": a[:7], "max_new_tokens": 6}) + "\n" +
+                       json.dumps({"tokens": b[:3]}) + "\n")
+    assert generate_cli.main(["--model", str(tmp_path), "--prompts", str(prompts), "--dtype", "float32",
+                              "--max-new-tokens", "4"]) == 0
+    lines = [json.loads(l) for l in capsys.readouterr().out.strip().split("\n")]
+
+    def oracle_greedy(prompt, n):
+        seq = list(prompt)
+        for _ in range(n):
+            seq.append(int(ko.forward(seq, W, cfg)[-1].argmax()))
+        return seq[len(prompt):]
+
+    assert lines == [{"id": "x", "tokens": oracle_greedy(a[:7], 6)}, {"id": "1", "tokens": oracle_greedy(b[:3], 4)}]
