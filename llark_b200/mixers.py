@@ -77,7 +77,8 @@ class GatedWindowAttention:
 
 class GatedLinearRecurrenceWeights:
     def __init__(self, w, pfx, spec, width, dev, act):
-        H, D, E = int(spec["heads"]), int(spec["dim"]), int(spec["vdim"])
+        H, D = int(spec["heads"]), int(spec["dim"])
+        E = int(spec.get("vdim", D))
         self.H, self.D, self.E = H, D, E
         self.w_qfv = torch.cat([_mat(w, pfx + "q", dev, act), _mat(w, pfx + "f", dev, act), _mat(w, pfx + "v", dev, act)])
         self.b_qfv = torch.cat([torch.zeros(H * D, device=dev, dtype=F32), _vec(w, pfx + "f.b", dev),

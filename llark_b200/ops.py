@@ -477,7 +477,8 @@ def _actf(dtype):
 
 
 # rows up to which a linear is the weight-streaming kernel (the activations then sit in L1 / L2, the op is a pure read
-# of the weight matrix); above it the tcgen05 GEMM core (bf16) or the tiled SIMT kernel (fp32 mode, odd shapes)
+# of the weight matrix); above it the tcgen05 GEMM core (bf16, at least one 64-wide tile in N and K, rows that TMA can
+# address) or the tiled SIMT kernel (fp32 mode, small or odd shapes)
 LINEAR_ROWS_MAX = 8
 LINEAR_STATS = {"rows": 0, "tcgen05": 0, "simt": 0}
 
@@ -503,7 +504,7 @@ def linear(a, w, bias=None, out_dtype=None, out=None):
         LINEAR_STATS["rows"] += 1
         check(lib().llark_linear_rows(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), c_fp32, _p(bias),
                                       M, N, K, in_fp32, _stream()), "linear_rows")
-    elif (not in_fp32 and K % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and out.stride(0) % vec == 0
+    elif (not in_fp32 and K >= 64 and N >= 64 and K % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and out.stride(0) % vec == 0
           and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0):
         LINEAR_STATS["tcgen05"] += 1
         gemm(a, w, bias=bias, out=out, M=M, N=N, K=K)
