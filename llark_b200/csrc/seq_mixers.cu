@@ -213,8 +213,8 @@ __global__ void glr_scan_kernel(const float* __restrict__ src, long long ld, int
                                 const int* __restrict__ item_row0, const int* __restrict__ item_n,
                                 const int* __restrict__ item_init, const int* __restrict__ item_final, int H, int D,
                                 int E, int R, int ecols) {
-    extern __shared__ float sm[];
-    constexpr int DPS = DPT + 1;  // padded row-group stride: the R groups of a column hit different banks
+    extern __shared__ __align__(16) float sm[];
+    constexpr int DPS = DPT + 4;  // padded row-group stride: 16-byte reads of the R groups of a column hit different banks
     const int DP = R * DPS;
     const int stage_floats = kTS * (3 * DP + ecols);
     const int h = blockIdx.y, b = blockIdx.z;
@@ -238,19 +238,17 @@ __global__ void glr_scan_kernel(const float* __restrict__ src, long long ld, int
     // stage layout: q[kTS][DP] | f[kTS][DP] | g[kTS][DP] | v[kTS][ecols]; raw q_pre / f_pre land in q / f
     auto issue = [&](int s, float* buf) {
         const int steps = n - s * kTS < kTS ? n - s * kTS : kTS;
-        for (int i = threadIdx.x; i < steps * D; i += blockDim.x) {
-            const int ts = i / D, d = i % D;
+        for (int ts = 0; ts < steps; ++ts) {
             const float* rowp = src + (long long)(row0 + s * kTS + ts) * ld;
-            const int at = ts * DP + (d / DPT) * DPS + (d % DPT);
-            cp_async4(buf + at, rowp + q_off + h * D + d);
-            cp_async4(buf + kTS * DP + at, rowp + f_off + h * D + d);
-        }
-        for (int i = threadIdx.x; i < steps * ecols; i += blockDim.x) {
-            const int ts = i / ecols, c = i % ecols;
-            const int ee = blockIdx.x * ecols + c;
-            if (ee < E)
-                cp_async4(buf + 3 * kTS * DP + ts * ecols + c,
-                          src + (long long)(row0 + s * kTS + ts) * ld + v_off + h * E + ee);
+            for (int d = threadIdx.x; d < D; d += blockDim.x) {
+                const int at = ts * DP + (d / DPT) * DPS + (d % DPT);
+                cp_async4(buf + at, rowp + q_off + h * D + d);
+                cp_async4(buf + kTS * DP + at, rowp + f_off + h * D + d);
+            }
+            for (int c = threadIdx.x; c < ecols; c += blockDim.x) {
+                const int ee = blockIdx.x * ecols + c;
+                if (ee < E) cp_async4(buf + 3 * kTS * DP + ts * ecols + c, rowp + v_off + h * E + ee);
+            }
         }
         cp_async_commit();
     };
@@ -261,20 +259,21 @@ __global__ void glr_scan_kernel(const float* __restrict__ src, long long ld, int
         cp_async_wait_all();
         __syncthreads();  // stage s has landed; everybody is done computing stage s - 1 (the other buffer)
         if (s + 1 < nstage) issue(s + 1, sm + ((s + 1) & 1) * stage_floats);
-        for (int i = threadIdx.x; i < steps * R * DPT; i += blockDim.x) {
-            const int ts = i / (R * DPT), d = i % (R * DPT);
-            const int at = ts * DP + (d / DPT) * DPS + (d % DPT);
-            float q = 0.f, f = 0.f, g = 0.f;
-            if (d < D) {
-                const float qp = buf[at], fp = buf[kTS * DP + at];
-                q = qp * sigmoidf_(qp);
-                const float lowv = lower ? lower[h * D + d] : 0.f;
-                f = lowv + (1.0f - lowv) * sigmoidf_(fp);
-                g = 1.0f - f;
+        for (int d = threadIdx.x; d < R * DPT; d += blockDim.x) {
+            const float lowv = (lower && d < D) ? lower[h * D + d] : 0.f;
+            for (int ts = 0; ts < steps; ++ts) {
+                const int at = ts * DP + (d / DPT) * DPS + (d % DPT);
+                float q = 0.f, f = 0.f, g = 0.f;  // padded rows: nothing kept, nothing written, nothing read out
+                if (d < D) {
+                    const float qp = buf[at], fp = buf[kTS * DP + at];
+                    q = qp * sigmoidf_(qp);
+                    f = lowv + (1.0f - lowv) * sigmoidf_(fp);
+                    g = 1.0f - f;
+                }
+                buf[at] = q;
+                buf[kTS * DP + at] = f;
+                buf[2 * kTS * DP + at] = g;
             }
-            buf[at] = q;
-            buf[kTS * DP + at] = f;
-            buf[2 * kTS * DP + at] = g;
         }
         __syncthreads();
         if (want_decay) {
@@ -292,17 +291,23 @@ __global__ void glr_scan_kernel(const float* __restrict__ src, long long ld, int
                 vt[c] = e0 + c < E ? buf[3 * kTS * DP + ts * ecols + ec * EC + c] : 0.f;
                 part[c] = 0.f;
             }
-            const float* q = buf + ts * DP + r * DPS;
-            const float* f = q + kTS * DP;
-            const float* g = f + kTS * DP;
+            const float4* q4 = reinterpret_cast<const float4*>(buf + ts * DP + r * DPS);
+            const float4* f4 = reinterpret_cast<const float4*>(buf + kTS * DP + ts * DP + r * DPS);
+            const float4* g4 = reinterpret_cast<const float4*>(buf + 2 * kTS * DP + ts * DP + r * DPS);
 #pragma unroll
-            for (int i = 0; i < DPT; ++i) {
-                const float fi = f[i], gi = g[i], qi = q[i];  // read once, used for all EC columns
+            for (int i4 = 0; i4 < DPT / 4; ++i4) {
+                const float4 fv = f4[i4], gv = g4[i4];  // read once, used for all EC columns
+                float4 qv = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (OUT) qv = q4[i4];
+                const float fa[4] = {fv.x, fv.y, fv.z, fv.w}, ga[4] = {gv.x, gv.y, gv.z, gv.w},
+                            qa[4] = {qv.x, qv.y, qv.z, qv.w};
 #pragma unroll
-                for (int c = 0; c < EC; ++c) {
-                    S[i][c] = fmaf(fi, S[i][c], gi * vt[c]);
-                    if (OUT) part[c] = fmaf(S[i][c], qi, part[c]);
-                }
+                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                    for (int c = 0; c < EC; ++c) {
+                        S[i4 * 4 + j][c] = fmaf(fa[j], S[i4 * 4 + j][c], ga[j] * vt[c]);
+                        if (OUT) part[c] = fmaf(S[i4 * 4 + j][c], qa[j], part[c]);
+                    }
             }
             if (OUT) {
 #pragma unroll
@@ -464,7 +469,7 @@ extern "C" int llark_seq_glr_scan(const float* src, long long ld, int q_off, int
         threads >>= 1;
         ecols >>= 1;
     }
-    const int DP = R * (dpt + 1);
+    const int DP = R * (dpt + 4);
     const size_t smem = sizeof(float) * 2 * (size_t)kTS * (3 * DP + ecols);
     dim3 grid((E + ecols - 1) / ecols, H, n_items);
 #define LLARK_GLR2(DPT_, EC_, OUT_)                                                                                        \

@@ -605,7 +605,7 @@ def seq_kv_ring_write(kn, vv, kring, vring, st, cap):
           "seq_kv_ring_write")
 
 
-GLR_CHUNK = 128        # rows per work item when a long prompt is scanned in chunks
+GLR_CHUNK = 256        # rows per work item when a long prompt is scanned in chunks
 GLR_CHUNK_MIN_LEN = 512  # shortest longest-request of a step that is scanned in chunks
 
 
