@@ -83,9 +83,44 @@ __global__ void qk_headnorm_kernel(const float* __restrict__ src, long long ld, 
     }
 }
 
+// N consecutive elements -> float, with one 4 / 8 / 16-byte load per piece when `vec` (the address is then aligned to
+// the piece); scalar loads otherwise.
+template <typename T, int N>
+__device__ __forceinline__ void load_run(const T* p, float (&out)[N], bool vec) {
+    constexpr int BYTES = N * (int)sizeof(T);
+    if (vec && BYTES >= 4) {
+        constexpr int PIECE = BYTES >= 16 ? 16 : BYTES;  // N is a power of two here
+        constexpr int PER = PIECE / (int)sizeof(T);
+#pragma unroll
+        for (int i = 0; i < N; i += PER) {
+            if constexpr (PIECE == 16) {
+                const uint4 v = *reinterpret_cast<const uint4*>(p + i);
+                const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+                for (int j = 0; j < PER; ++j) out[i + j] = ldf(e + j);
+            } else if constexpr (PIECE == 8) {
+                const uint2 v = *reinterpret_cast<const uint2*>(p + i);
+                const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+                for (int j = 0; j < PER; ++j) out[i + j] = ldf(e + j);
+            } else {
+                const uint32_t v = *reinterpret_cast<const uint32_t*>(p + i);
+                const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+                for (int j = 0; j < PER; ++j) out[i + j] = ldf(e + j);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) out[i] = ldf(p + i);
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ windowed attention
 // Block per (token, head); its warps take the 32-key tiles of the window round-robin, each with its own online softmax,
-// and are merged at the end. Lane = key while scoring, lane = output channel while accumulating. DPL = ceil(E / 32).
+// and are merged at the end. Lane = key while scoring (the key row is read in 16-byte pieces when it is aligned),
+// lane = DPL adjacent output channels while accumulating (one load of DPL elements per key when E = 32 * DPL; channels
+// lane + 32 i otherwise). DPL = ceil(E / 32) rounded up to a power of two.
 template <typename T, int DPL>
 __global__ void swa_attn_kernel(const T* __restrict__ qn, const T* __restrict__ kn, const T* __restrict__ vv,
                                 const T* __restrict__ kring, const T* __restrict__ vring, const float* __restrict__ gate,
@@ -112,6 +147,9 @@ __global__ void swa_attn_kernel(const T* __restrict__ qn, const T* __restrict__ 
     __syncthreads();
     const long long ring_base = (long long)slot[b] * cap;
     const long long first_here = from_ring_only ? p + 1 : p0;  // positions >= first_here are rows of this step
+    constexpr int KV = 16 / (int)sizeof(T);  // elements of a 16-byte piece of a key row
+    const bool kvec = (D % KV) == 0;         // rows then start on 16-byte boundaries (torch allocations are 256-byte aligned)
+    const bool vvec = DPL > 1 && E == 32 * DPL;
     float m = -INFINITY, l = 0.f, acc[DPL];
 #pragma unroll
     for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
@@ -123,7 +161,16 @@ __global__ void swa_attn_kernel(const T* __restrict__ qn, const T* __restrict__ 
             const T* kr = j >= first_here ? kn + ((long long)(cu[b] + (j - p0)) * G + g) * D
                                           : kring + ((ring_base + (j % cap)) * G + g) * D;
             float dot = 0.f;
-            for (int d = 0; d < D; ++d) dot = fmaf(sq[d], ldf(kr + d), dot);
+            if (kvec) {
+                for (int d = 0; d < D; d += KV) {
+                    float kk[KV];
+                    load_run<T, KV>(kr + d, kk, true);
+#pragma unroll
+                    for (int x = 0; x < KV; ++x) dot = fmaf(sq[d + x], kk[x], dot);
+                }
+            } else {
+                for (int d = 0; d < D; ++d) dot = fmaf(sq[d], ldf(kr + d), dot);
+            }
             s = dot * sc;
         }
         const float mt = warp_max(s);
@@ -142,10 +189,17 @@ __global__ void swa_attn_kernel(const T* __restrict__ qn, const T* __restrict__ 
             const T* vr = j2 >= first_here ? vv + ((long long)(cu[b] + (j2 - p0)) * G + g) * E
                                            : vring + ((ring_base + (j2 % cap)) * G + g) * E;
             const float pk = sp[warp * 32 + k];
+            if (vvec) {
+                float vx[DPL];
+                load_run<T, DPL>(vr + lane * DPL, vx, true);
 #pragma unroll
-            for (int i = 0; i < DPL; ++i) {
-                const int e = lane + 32 * i;
-                if (e < E) acc[i] = fmaf(pk, ldf(vr + e), acc[i]);
+                for (int i = 0; i < DPL; ++i) acc[i] = fmaf(pk, vx[i], acc[i]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < DPL; ++i) {
+                    const int e = lane + 32 * i;
+                    if (e < E) acc[i] = fmaf(pk, ldf(vr + e), acc[i]);
+                }
             }
         }
         __syncwarp();
@@ -156,7 +210,7 @@ __global__ void swa_attn_kernel(const T* __restrict__ qn, const T* __restrict__ 
     }
 #pragma unroll
     for (int i = 0; i < DPL; ++i) {
-        const int e = lane + 32 * i;
+        const int e = vvec ? lane * DPL + i : lane + 32 * i;
         if (e < E) sacc[warp * E + e] = acc[i];
     }
     __syncthreads();

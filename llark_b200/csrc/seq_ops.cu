@@ -14,7 +14,7 @@
 //   llark_seq_add_rmsnorm   x_out = x + rmsnorm(y) * w   (norm on the sublayer's output), optional ACT copy of x_out
 //   llark_seq_rmsnorm_rows  y[i] = rmsnorm(x[rows[i]]) * w -> ACT (final norm of the rows whose logits are wanted)
 //   llark_seq_relu2         y = relu(u)^2
-//   llark_linear_rows       C = A W^T (+ bias) for a handful of rows: weight-streaming, one warp per output column
+//   llark_linear_rows       C = A W^T (+ bias) for a handful of rows: weight-streaming, one or two output columns per warp
 //   llark_linear_simt       C = A W^T (+ bias), any shape, tiled SIMT with fp32 accumulation (the fp32 mode's GEMM and the
 //                           fallback for shapes the TMA descriptors of the tcgen05 core cannot take)
 #include "common.cuh"
@@ -298,49 +298,65 @@ __global__ void relu2_kernel(const T* __restrict__ u, T* __restrict__ y, long lo
 }
 
 // ------------------------------------------------------------------------------------------------ linears
-// Few rows (decode): warp per output column, lanes stride over K, the rows of A come from L1 / L2.
-template <typename T, typename TC, int MB>
+// Few rows (decode): a warp owns NC adjacent output columns, its lanes stride over K in 16-byte pieces (streamed,
+// evict-first), the rows of A come from L1 / L2 and are read once per NC weight pieces.
+template <typename T, typename TC, int MB, int NC>
 __global__ void __launch_bounds__(256)
 linear_rows_kernel(const T* __restrict__ A, long long lda, const T* __restrict__ W, long long ldw, TC* __restrict__ Cm,
                    long long ldc, const float* __restrict__ bias, int M, int N, int K, int vec_ok) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long n = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+    const long long n0 = ((long long)blockIdx.x * (blockDim.x >> 5) + warp) * NC;
     const int m0 = blockIdx.y * MB;
-    if (n >= N) return;
-    float acc[MB];
+    if (n0 >= N) return;
+    float acc[MB][NC];
 #pragma unroll
-    for (int m = 0; m < MB; ++m) acc[m] = 0.f;
-    const T* wr = W + n * ldw;
+    for (int m = 0; m < MB; ++m)
+#pragma unroll
+        for (int c = 0; c < NC; ++c) acc[m][c] = 0.f;
+    const T* wr[NC];
+#pragma unroll
+    for (int c = 0; c < NC; ++c) wr[c] = W + (n0 + c < N ? n0 + c : (long long)N - 1) * ldw;  // tail: re-read, never stored
     constexpr int VEC = 16 / (int)sizeof(T);
     int k0 = 0;
     if (vec_ok) {
         const int kv = K / VEC;
         for (int v = lane; v < kv; v += 32) {
-            const uint4 wv = __ldcs(reinterpret_cast<const uint4*>(wr) + v);
-            const T* wp = reinterpret_cast<const T*>(&wv);
+            uint4 wv[NC];
+#pragma unroll
+            for (int c = 0; c < NC; ++c) wv[c] = __ldcs(reinterpret_cast<const uint4*>(wr[c]) + v);
 #pragma unroll
             for (int m = 0; m < MB; ++m) {
                 if (m0 + m < M) {
                     const uint4 av = __ldg(reinterpret_cast<const uint4*>(A + (long long)(m0 + m) * lda) + v);
                     const T* ap = reinterpret_cast<const T*>(&av);
 #pragma unroll
-                    for (int e = 0; e < VEC; ++e) acc[m] = fmaf(ldf(ap + e), ldf(wp + e), acc[m]);
+                    for (int c = 0; c < NC; ++c) {
+                        const T* wp = reinterpret_cast<const T*>(&wv[c]);
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) acc[m][c] = fmaf(ldf(ap + e), ldf(wp + e), acc[m][c]);
+                    }
                 }
             }
         }
         k0 = kv * VEC;
     }
     for (int k = k0 + lane; k < K; k += 32) {
-        const float wv = ldf(wr + k);
 #pragma unroll
-        for (int m = 0; m < MB; ++m)
-            if (m0 + m < M) acc[m] = fmaf(ldf(A + (long long)(m0 + m) * lda + k), wv, acc[m]);
+        for (int c = 0; c < NC; ++c) {
+            const float wv = ldf(wr[c] + k);
+#pragma unroll
+            for (int m = 0; m < MB; ++m)
+                if (m0 + m < M) acc[m][c] = fmaf(ldf(A + (long long)(m0 + m) * lda + k), wv, acc[m][c]);
+        }
     }
 #pragma unroll
-    for (int m = 0; m < MB; ++m) {
-        const float s = warp_sum(acc[m]);
-        if (lane == 0 && m0 + m < M) stf(Cm + (long long)(m0 + m) * ldc + n, s + (bias ? bias[n] : 0.f));
-    }
+    for (int m = 0; m < MB; ++m)
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+            const float s = warp_sum(acc[m][c]);
+            if (lane == 0 && m0 + m < M && n0 + c < N)
+                stf(Cm + (long long)(m0 + m) * ldc + n0 + c, s + (bias ? bias[n0 + c] : 0.f));
+        }
 }
 
 // Any shape: 64 x 64 tile, 16-deep k slices through shared memory, 4 x 4 outputs per thread, fp32 FMA.
@@ -498,16 +514,21 @@ static void launch_rows(const void* A, long long lda, const void* W, long long l
     const int vec_ok = (K % vec == 0) && (lda % vec == 0) && (ldw % vec == 0) &&
                        (((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) == 0);
     const int warps = 8;
-    const unsigned gx = (unsigned)((N + warps - 1) / warps);
+    // two columns per warp once that still leaves several warps per SM (148 SMs); one for narrow outputs
+    const bool two = (long long)N >= 2LL * warps * 148 * 2;
+    const int nc = two ? 2 : 1;
+    const unsigned gx = (unsigned)((N + warps * nc - 1) / (warps * nc));
+#define LLARK_ROWS(MB_, NC_)                                                                                            \
+    linear_rows_kernel<T, TC, MB_, NC_><<<dim3(gx, (M + MB_ - 1) / MB_), warps * 32, 0, st>>>(                          \
+        (const T*)A, lda, (const T*)W, ldw, (TC*)C, ldc, bias, M, N, K, vec_ok)
     if (M <= 2) {
-        dim3 grid(gx, (M + 1) / 2);
-        linear_rows_kernel<T, TC, 2><<<grid, warps * 32, 0, st>>>((const T*)A, lda, (const T*)W, ldw, (TC*)C, ldc, bias, M,
-                                                                  N, K, vec_ok);
+        if (two) LLARK_ROWS(2, 2);
+        else LLARK_ROWS(2, 1);
     } else {
-        dim3 grid(gx, (M + 7) / 8);
-        linear_rows_kernel<T, TC, 8><<<grid, warps * 32, 0, st>>>((const T*)A, lda, (const T*)W, ldw, (TC*)C, ldc, bias, M,
-                                                                  N, K, vec_ok);
+        if (two) LLARK_ROWS(8, 2);
+        else LLARK_ROWS(8, 1);
     }
+#undef LLARK_ROWS
 }
 
 extern "C" int llark_linear_rows(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc,

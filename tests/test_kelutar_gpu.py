@@ -89,7 +89,8 @@ def _tokens(n, vocab, seed):
 
 # ------------------------------------------------------------------------------------------------ mechanisms alone
 @pytest.mark.parametrize("M,N,K", [(1, 50, 72), (3, 97, 100), (8, 64, 33), (23, 96, 72), (40, 97, 72), (130, 200, 64),
-                                   (17, 24, 7), (20, 64, 16), (9, 8, 8), (300, 64, 64), (65, 72, 320)])
+                                   (17, 24, 7), (20, 64, 16), (9, 8, 8), (300, 64, 64), (65, 72, 320),
+                                   (3, 4800, 72), (1, 4737, 64), (8, 4739, 33)])
 @pytest.mark.parametrize("dtype", [F32, BF16])
 def test_linear_every_route(M, N, K, dtype):
     from llark_b200 import ops
