@@ -150,7 +150,7 @@ def _nbytes(x):
     return 0
 
 
-def _work(name, a, k, out, ctx):
+def _op_work(name, a, k, out, ctx):
     """(algorithmic bytes, FLOPs) of one recorded call. Stores that are only partly touched (rings, states, KV caches)
     are counted by what the op has to read and write, the rest by the tensors handed in and out."""
     if name in ("linear", "gemm", "gemv"):
@@ -196,7 +196,7 @@ def op_table(records, ctx, peaks):
         if name == "gemm" and ctx.get("skip_gemm"):
             continue  # already inside `linear`
         ms = e0.elapsed_time(e1)
-        nb, flops = _work(name, a, k, out, ctx)
+        nb, flops = _op_work(name, a, k, out, ctx)
         if name == "linear":
             name = "linear_rows" if a[0].shape[0] <= 8 else "linear_tcgen05"
         if name == "gemm":
