@@ -71,6 +71,9 @@ CONFIGS = {
     # head sizes the tensor-core attention takes (multiples of 16), a window wider than one key tile, three taps
     "tc_heads": _cfg([_at(4, 2, 32, 70, mlp=FF), _hg(2, 32, 48), _at(4, 2, 32, 70, mlp=FF, weights_of=0),
                       _at(2, 2, 64, 3)], vocab=120, width=64, taps=3),
+    # nothing is a multiple of 4: every op takes its scalar route, the linears the tiled SIMT kernel
+    "odd_sizes": _cfg([_hg(3, 10, 7), _at(3, 1, 10, 4, mlp={"kind": "dense", "ff": 21}), _hg(1, 5, 33)],
+                      vocab=33, width=50, taps=3, max_positions=130),
     # two taps, one head, head sizes above 32 and 128
     "wide_heads": _cfg([_hg(2, 144, 40), _at(1, 1, 72, 5, scale=0.2, mlp=FF)], vocab=50, width=80, taps=2),
 }
