@@ -146,6 +146,8 @@ __global__ void swa_attn_kernel(const T* __restrict__ qn, const T* __restrict__ 
     for (int d = threadIdx.x; d < D; d += blockDim.x) sq[d] = ldf(qn + ((long long)t * H + h) * D + d);
     __syncthreads();
     const long long ring_base = (long long)slot[b] * cap;
+    const int ring0 = (int)(lo % cap);  // ring entry of the window's first key; key jj sits at ring0 + jj (- cap), as
+                                        // the keys of a window never outnumber the ring's entries
     const long long first_here = from_ring_only ? p + 1 : p0;  // positions >= first_here are rows of this step
     constexpr int KV = 16 / (int)sizeof(T);  // elements of a 16-byte piece of a key row
     const bool kvec = (D % KV) == 0;         // rows then start on 16-byte boundaries (torch allocations are 256-byte aligned)
@@ -158,8 +160,10 @@ __global__ void swa_attn_kernel(const T* __restrict__ qn, const T* __restrict__ 
         const long long j = lo + jj;
         float s = -INFINITY;
         if (jj < nkeys) {
+            int ridx = ring0 + jj;
+            if (ridx >= cap) ridx -= cap;
             const T* kr = j >= first_here ? kn + ((long long)(cu[b] + (j - p0)) * G + g) * D
-                                          : kring + ((ring_base + (j % cap)) * G + g) * D;
+                                          : kring + ((ring_base + ridx) * G + g) * D;
             float dot = 0.f;
             if (kvec) {
                 for (int d = 0; d < D; d += KV) {
@@ -186,8 +190,10 @@ __global__ void swa_attn_kernel(const T* __restrict__ qn, const T* __restrict__ 
         const int cnt = nkeys - tile * 32 < 32 ? nkeys - tile * 32 : 32;
         for (int k = 0; k < cnt; ++k) {
             const long long j2 = lo + tile * 32 + k;
+            int ridx = ring0 + tile * 32 + k;
+            if (ridx >= cap) ridx -= cap;
             const T* vr = j2 >= first_here ? vv + ((long long)(cu[b] + (j2 - p0)) * G + g) * E
-                                           : vring + ((ring_base + (j2 % cap)) * G + g) * E;
+                                           : vring + ((ring_base + ridx) * G + g) * E;
             const float pk = sp[warp * 32 + k];
             if (vvec) {
                 float vx[DPL];

@@ -6,7 +6,7 @@
 // queries. A key at position j of the sequence comes from the step's own buffers when j >= pos0 (it arrived with this
 // step) and from ring entry j % cap of the request's slot otherwise. Q, K and V tiles sit in shared memory row-major and
 // reach the registers through ldmatrix (V through ldmatrix.trans); the row pitch (+8 elements) keeps those
-// conflict-free. Per-head score scale (softmax scale x temperature) and the optional sigmoid output gate are applied
+// conflict-free. K / V tiles are double-buffered: the next tile is in flight (cp.async) while this one is multiplied. Per-head score scale (softmax scale x temperature) and the optional sigmoid output gate are applied
 // in registers. The SIMT kernel of seq_mixers.cu remains the path for single-token steps, fp32 and head
 // sizes that are not multiples of 16.
 #include "common.cuh"
@@ -26,6 +26,9 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
@@ -53,8 +56,9 @@ swa_mma_kernel(const bf16_t* __restrict__ qn, const bf16_t* __restrict__ kn, con
     extern __shared__ __align__(16) unsigned char smraw[];
     const int DS = D + 8;                           // row pitch: 16 bytes more than the row, so that the eight
     bf16_t* sQ = reinterpret_cast<bf16_t*>(smraw);  // [BQ][DS]   rows of an ldmatrix fall into different banks
-    bf16_t* sK = sQ + BQ * DS;                      // [BK][DS]
-    bf16_t* sV = sK + BK * DS;                      // [BK][DS]   row-major; P.V reads it through ldmatrix.trans
+    bf16_t* sK0 = sQ + BQ * DS;                     // [2][BK][DS]  two stages: the next tile arrives by cp.async
+    bf16_t* sV0 = sK0 + 2 * BK * DS;                // [2][BK][DS]  while this one is multiplied; row-major, P.V reads
+                                                    //              it through ldmatrix.trans
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
     const int dv = D >> 3;  // 16-byte vectors per row
 
@@ -68,7 +72,7 @@ swa_mma_kernel(const bf16_t* __restrict__ qn, const bf16_t* __restrict__ kn, con
     const long long pq_lo = p0 + qt0, pq_hi = p0 + q_last;
     const long long k_lo = pq_lo - window + 1 > 0 ? pq_lo - window + 1 : 0;
     const long long ring_base = (long long)slot[b] * cap;
-    const float sc = scale_h[h];
+    const float sc = scale_h[h] * 1.4426950408889634f;  // scores in units of log2: softmax through exp2
 
     float o[DMAX / 8][4];
 #pragma unroll
@@ -76,23 +80,57 @@ swa_mma_kernel(const bf16_t* __restrict__ qn, const bf16_t* __restrict__ kn, con
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     const int qrow = warp * 16 + gq;  // this thread's rows: qrow and qrow + 8
 
-    for (long long kt = k_lo; kt <= pq_hi; kt += BK) {
-        __syncthreads();  // the previous tile's fragments have been read (and sQ is written on the first pass)
-        for (int i = threadIdx.x; i < BK * dv; i += blockDim.x) {
-            const int r = i / dv, c = (i % dv) * 8;
+    // A key before this step sits in ring entry (position % cap). Those keys are fewer than cap positions past k_lo, so
+    // their entry is ring0 + (position - k_lo), minus cap once if it runs over: no division in the loop. The walk over
+    // (row, 16-byte piece) advances by the CTA's 128 threads without dividing either.
+    const int ring0 = (int)(k_lo % cap);
+    const int step_r = (int)blockDim.x / dv, step_c = (int)blockDim.x % dv;
+    const int my_r0 = (int)threadIdx.x / dv, my_c0 = (int)threadIdx.x % dv;
+    auto load_tile = [&](long long kt, int stage) {
+        bf16_t* dk = sK0 + stage * BK * DS;
+        bf16_t* dvp = sV0 + stage * BK * DS;
+        int r = my_r0, cp = my_c0;
+        while (r < BK) {
+            const int c = cp * 8;
             const long long j = kt + r;
-            uint4 kq = make_uint4(0, 0, 0, 0), vq = make_uint4(0, 0, 0, 0);
             if (j <= pq_hi) {
-                const long long e = j >= p0 ? ((long long)(row0 + (j - p0)) * G + g) : ((ring_base + (j % cap)) * G + g);
-                const bf16_t* kp = (j >= p0 ? kn : kring) + e * D + c;
-                const bf16_t* vp = (j >= p0 ? vv : vring) + e * D + c;
-                kq = *reinterpret_cast<const uint4*>(kp);
-                vq = *reinterpret_cast<const uint4*>(vp);
+                if (j >= p0) {
+                    const long long e = (long long)(row0 + (int)(j - p0)) * G + g;
+                    cp_async16(dk + r * DS + c, kn + e * D + c);
+                    cp_async16(dvp + r * DS + c, vv + e * D + c);
+                } else {
+                    int idx = ring0 + (int)(j - k_lo);
+                    if (idx >= cap) idx -= cap;
+                    const long long e = (ring_base + idx) * G + g;
+                    cp_async16(dk + r * DS + c, kring + e * D + c);
+                    cp_async16(dvp + r * DS + c, vring + e * D + c);
+                }
+            } else {
+                *reinterpret_cast<uint4*>(dk + r * DS + c) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(dvp + r * DS + c) = make_uint4(0, 0, 0, 0);
             }
-            *reinterpret_cast<uint4*>(sK + r * DS + c) = kq;
-            *reinterpret_cast<uint4*>(sV + r * DS + c) = vq;
+            r += step_r;
+            cp += step_c;
+            if (cp >= dv) {
+                cp -= dv;
+                ++r;
+            }
         }
-        __syncthreads();
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int n_tiles = (int)((pq_hi - k_lo) / BK) + 1;
+    load_tile(k_lo, 0);
+    for (int it = 0; it < n_tiles; ++it) {
+        const long long kt = k_lo + (long long)it * BK;
+        if (it + 1 < n_tiles) {
+            load_tile(kt + BK, (it + 1) & 1);  // that stage was released by the barrier at the end of the last pass
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();  // tile `it` (and, on the first pass, sQ) is in shared memory for everybody
+        const bf16_t* sK = sK0 + (it & 1) * BK * DS;
+        const bf16_t* sV = sV0 + (it & 1) * BK * DS;
         // ---- S = Q K^T for this warp's 16 rows x 64 keys
         float s[BK / 8][4];
 #pragma unroll
@@ -115,23 +153,41 @@ swa_mma_kernel(const bf16_t* __restrict__ qn, const bf16_t* __restrict__ kn, con
         }
         // ---- scale, mask (causal and window), online softmax in fp32
         float mt[2] = {-INFINITY, -INFINITY};
+        // rel = query position - first key of the tile: key column c is visible iff c <= rel and rel - c < window.
+        // A tile whose 64 keys are visible to all 16 rows of the warp (the usual case inside a wide window) skips the test.
+        const long long rel_lo = pq_lo + warp * 16 - kt;  // rel of the warp's first row; its rows are consecutive
+        const bool rows_ok = qt0 + warp * 16 + 15 < n;
+        const bool interior = rows_ok && rel_lo >= BK - 1 && rel_lo + 15 < window;
+        if (interior) {
 #pragma unroll
-        for (int nt = 0; nt < BK / 8; ++nt)
+            for (int nt = 0; nt < BK / 8; ++nt)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int r = qrow + (e >> 1) * 8;
-                const long long qp = p0 + qt0 + r, kp = kt + nt * 8 + 2 * tq + (e & 1);
-                const bool ok = (qt0 + r < n) && kp <= qp && qp - kp < window;
-                s[nt][e] = ok ? s[nt][e] * sc : -INFINITY;
-                mt[e >> 1] = fmaxf(mt[e >> 1], s[nt][e]);
-            }
+                for (int e = 0; e < 4; ++e) {
+                    s[nt][e] *= sc;
+                    mt[e >> 1] = fmaxf(mt[e >> 1], s[nt][e]);
+                }
+        } else {
+            // clamp so that the 32-bit arithmetic below cannot overflow: beyond +-2^30 the answer is the same
+            const long long rl = rel_lo + gq;
+            const int rel0 = (int)(rl > (1LL << 30) ? (1LL << 30) : (rl < -(1LL << 30) ? -(1LL << 30) : rl));
+#pragma unroll
+            for (int nt = 0; nt < BK / 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int x = e >> 1;
+                    const int rel = rel0 + x * 8, c = nt * 8 + 2 * tq + (e & 1);
+                    const bool ok = (qt0 + qrow + x * 8 < n) && c <= rel && rel - c < window;
+                    s[nt][e] = ok ? s[nt][e] * sc : -INFINITY;
+                    mt[x] = fmaxf(mt[x], s[nt][e]);
+                }
+        }
         float alpha[2], mn[2];
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
             mt[x] = fmaxf(mt[x], __shfl_xor_sync(0xffffffffu, mt[x], 1));
             mt[x] = fmaxf(mt[x], __shfl_xor_sync(0xffffffffu, mt[x], 2));
             mn[x] = fmaxf(m[x], mt[x]);
-            alpha[x] = mn[x] == -INFINITY ? 1.f : expf(m[x] - mn[x]);
+            alpha[x] = mn[x] == -INFINITY ? 1.f : exp2f(m[x] - mn[x]);
             m[x] = mn[x];
             l[x] *= alpha[x];
         }
@@ -140,7 +196,7 @@ swa_mma_kernel(const bf16_t* __restrict__ qn, const bf16_t* __restrict__ kn, con
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int x = e >> 1;
-                const float p = mn[x] == -INFINITY ? 0.f : expf(s[nt][e] - mn[x]);
+                const float p = mn[x] == -INFINITY ? 0.f : exp2f(s[nt][e] - mn[x]);
                 s[nt][e] = p;
                 l[x] += p;
             }
@@ -169,6 +225,7 @@ swa_mma_kernel(const bf16_t* __restrict__ qn, const bf16_t* __restrict__ kn, con
                 }
             }
         }
+        __syncthreads();  // everybody is done with this stage before the pass after next refills it
     }
     // ---- normalise, gate, store
 #pragma unroll
@@ -202,7 +259,7 @@ template <int DMAX>
 static int launch(const void* qn, const void* kn, const void* vv, const void* kring, const void* vring,
                   const float* gate, long long gate_ld, const float* scale_h, void* out, const int* cu, const int* pos0,
                   const int* slot, int n_seq, int max_len, int H, int G, int D, int window, int cap, cudaStream_t st) {
-    const size_t smem = sizeof(bf16_t) * (size_t)(BQ + 2 * BK) * (D + 8);
+    const size_t smem = sizeof(bf16_t) * (size_t)(BQ + 4 * BK) * (D + 8);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(swa_mma_kernel<DMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) {
