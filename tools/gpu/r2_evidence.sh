@@ -4,7 +4,7 @@
 #   1. ncu launch list of one bench step (shares per kernel)                         -> <tag>_launches.csv
 #   2. per-launch DRAM bytes + duration of every GEMM of the bench's own shapes      -> <tag>_gemm_dram.csv + <tag>_gemm_shapes.json
 #   3. ncu --set full of the HBM-bound kernels and the attention kernels, of the GEMM kinds, of the Jukebox kernels and of
-#      the prior's four GEMMs (with source-level stall samples)                        -> <tag>_*_full.md / _hbm.md / _source.csv
+#      the prior's four GEMMs                                          -> <tag>_*_full.md / _hbm.md
 #   4. (optional, SAN=1) compute-sanitizer memcheck over the small-shape kernel tests -> <tag>_memcheck.txt
 # usage: gpurun --timeout 2400 -- 'bash tools/gpu/r2_evidence.sh r2f'
 mkdir -p gpurun_out
@@ -36,19 +36,10 @@ timeout 900 ncu --set full --clock-control none \
   > gpurun_out/${TAG}_ncu_jukebox.log 2>&1
 summ ${TAG}_prof_jukebox
 # the prior's four GEMMs of block 0 (c_attn fp32 out, c_proj fp32 out + fp32 residual, fc bf16 quick-GELU, fc_proj) with
-# source-level stall samples: where does the fp32 epilogue wait?
-timeout 900 ncu --set full --clock-control none --import-source on -k regex:gemm2_kernel -c 4 \
+# the full counter set
+timeout 900 ncu --set full --clock-control none -k regex:gemm2_kernel -c 4 \
   -o gpurun_out/${TAG}_prof_prior_gemm python tools/bench_jukebox.py --precision bf16 --depth 1 --steps 1 --warmup 0 \
   > gpurun_out/${TAG}_ncu_prior_gemm.log 2>&1
-ncu -i gpurun_out/${TAG}_prof_prior_gemm.ncu-rep --page source --csv > gpurun_out/${TAG}_prior_gemm_source_all.csv 2>/dev/null
-python - <<PY
-import csv, io
-rows = list(csv.reader(open("gpurun_out/${TAG}_prior_gemm_source_all.csv", errors="replace")))
-hdr = next((r for r in rows if "Source" in r or "# Samples" in " ".join(r)), None)
-print("source page columns:", hdr[:30] if hdr else None, "rows", len(rows))
-PY
-head -c 3000000 gpurun_out/${TAG}_prior_gemm_source_all.csv > gpurun_out/${TAG}_prior_gemm_source.csv
-rm -f gpurun_out/${TAG}_prior_gemm_source_all.csv
 summ ${TAG}_prof_prior_gemm
 if [ "${SAN:-0}" = "1" ]; then
 SMALL='not 8192 and not 4096 and not 2048 and not 4160 and not many_tiles and not llama7b and not full_geometry and not real_head_shape'
