@@ -7,7 +7,8 @@ OBJ := $(patsubst llark_b200/csrc/%.cu,build/%.o,$(SRC))
 LIB := llark_b200/libllark_b200.so
 
 # the subset a native checkpoint of a layer-list decoder needs: GEMM core, decode linears, generation-path ops
-SERVE_OBJ := build/gemm_tcgen05.o build/gemv.o build/seq_ops.o build/seq_mixers.o build/seq_swa_mma.o
+SERVE_OBJ := build/gemm_tcgen05.o build/gemv.o build/seq_ops.o build/seq_mixers.o build/seq_swa_mma.o build/seq_delta.o \
+             build/seq_latent.o build/seq_moe.o
 LIB_SERVE := llark_b200/libllark_serve.so
 
 all: $(LIB)

@@ -339,6 +339,58 @@ int llark_seq_glr_combine(const float* state, float* chunk_state, const float* c
 int llark_seq_head_rmsnorm(const float* x, const float* w, void* out, long long n_rows, int E, float eps, int act_fp32,
                            cudaStream_t stream);
 
+/* ---- further parts of layer-list decoders: grouped RMS norm, parallel-sublayer residual, delta-rule recurrences
+ * (csrc/seq_delta.cu), latent attention (csrc/seq_latent.cu), routed mixture of experts (csrc/seq_moe.cu) ---- */
+/* y = A W^T (+ bias) with fp32 weights and bf16 or fp32 activations, fp32 output (router logits) */
+int llark_linear_simt_w32(const void* A, long long lda, const float* W, long long ldw, float* C, long long ldc,
+                          const float* bias, int M, int N, int K, int in_fp32, cudaStream_t stream);
+/* out[r] = norm of x[rows ? rows[r] : r] (+ add_vec) in `groups` equal consecutive parts, each divided by its own
+ * sqrt(mean(part^2) + eps), times w; with x_out (rows == NULL) the sum x + add_vec is written too */
+int llark_seq_group_rmsnorm(const float* x, const int* rows, const float* add_vec, float* x_out, const float* w, void* out,
+                            int n_rows, int C, int groups, float eps, int out_fp32, cudaStream_t stream);
+/* x_out = x + (y + sum_k wts[t, k] * z[pos_of[t * top + k]]); top = 0: x + y */
+int llark_seq_residual_combine(const float* x, const float* y, const float* z, const int* pos_of, const float* wts,
+                               int top, float* x_out, int n_tok, int C, cudaStream_t stream);
+/* out[t, c] = act(sum_j w[c, j] * src[t - taps + 1 + j, c]) over n_ch columns of a strided fp32 matrix (src points at the
+ * first column); carry fp32 [slots, taps-1, n_ch] holds each request's last inputs and is refreshed */
+int llark_seq_conv_act(const float* src, long long ld, const float* w, float* carry, const int* tok_seq, const int* cu,
+                       const int* slot, float* out, int n_tok, int n_seq, int n_ch, int taps, int silu,
+                       cudaStream_t stream);
+/* the five vectors {q, z, d, p1, p2} [n_tok, H, 5, D] of the delta-rule scan; rule 0: gated delta rule, rule 1:
+ * generalized delta rule (see csrc/seq_delta.cu) */
+int llark_seq_delta_prep(int rule, const float* q, long long q_ld, const float* k, long long k_ld, const float* dec,
+                         long long dec_ld, const float* dec_bias, const float* rate_log, const float* mix,
+                         long long mix_ld, float* vec, int n_tok, int H, int G, int D, float unit_eps,
+                         cudaStream_t stream);
+/* S[:, e] = d S[:, e] + p1 (z . S[:, e]) + p2 v[e], o[e] = q . S[:, e] per token; state fp32 [slots, H, D, E] */
+int llark_seq_delta_scan(const float* vec, const float* v, long long v_ld, float* state, float* o, const int* cu,
+                         const int* slot, int n_seq, int H, int D, int E, cudaStream_t stream);
+/* per-head RMS norm of x fp32 [n_tok, H, E], times w ([E] shared or [H, E]), times sigmoid(gate) -> ACT */
+int llark_seq_head_norm_gate(const float* x, const float* w, int w_per_head, const float* gate, long long gate_ld,
+                             void* out, long long n_tok, int H, int E, float eps, int act_fp32, cudaStream_t stream);
+/* latent attention: normed latent and rotated shared key part -> ckr ACT [n_tok, R + P] (and the ring row of the
+ * token's position when ring != NULL), rotated query parts -> qf ACT [n_tok, H, R + P] columns R.. */
+int llark_seq_latent_prep(const float* q, long long q_ld, const float* lat, long long lat_ld, const float* norm_w,
+                          const float* freqs, int n_rot, float mult, void* ckr, void* qf, void* ring, const int* tok_seq,
+                          const int* cu, const int* pos0, const int* slot, int n_tok, int H, int Dn, int P, int R, int cap,
+                          float eps, int act_fp32, cudaStream_t stream);
+/* y[m, h * y_hs + n] = sum_k x[m, h * x_hs + k] * w[h][n][k] (* sigmoid(gate[m, h * N + n])) */
+int llark_seq_head_linear(const void* x, int x_fp32, long long ldx, int x_hs, const void* w, void* y, long long ldy,
+                          int y_hs, const float* gate, long long gate_ld, int M, int H, int N, int K, int act_fp32,
+                          cudaStream_t stream);
+/* y = tanh(u), fp32 in, ACT out */
+int llark_seq_tanh(const float* u, void* y, long long n, int act_fp32, cudaStream_t stream);
+/* routed mixture of experts (see csrc/seq_moe.cu) */
+int llark_seq_moe_route(const float* logits, long long ld, int* ids, float* wts, int n_tok, int n_exp, int n_groups,
+                        int keep, int top, float scale, cudaStream_t stream);
+int llark_seq_moe_tile_rows(void);
+int llark_seq_moe_sort(const int* ids, int n_ent, int n_exp, int* perm, int* pos_of, int* tiles, int* meta,
+                       cudaStream_t stream);
+int llark_seq_moe_up(const void* x, long long ldx, const int* perm, int top, const void* w_gate_up, void* act,
+                     const int* tiles, const int* meta, int max_tiles, int ff, int K, int act_fp32, cudaStream_t stream);
+int llark_seq_moe_down(const void* act, const void* w_down, float* z, const int* tiles, const int* meta, int max_tiles,
+                       int C, int ff, int act_fp32, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -15,12 +15,16 @@ SERVE_LIB_PATH = os.path.join(_HERE, "libllark_serve.so")
 
 _ERR = {-1: "LLARK_EINVAL (bad shape/alignment/argument)", -2: "LLARK_ECUDA", -3: "LLARK_EDRIVER", -4: "LLARK_ENCCL"}
 
-# the generation path of layer-list decoders (csrc/seq_ops.cu, csrc/seq_mixers.cu)
+# the generation path of layer-list decoders (csrc/seq_*.cu)
 SEQ_SYMBOLS = [
     "llark_seq_embed", "llark_seq_short_conv", "llark_seq_conv_tail", "llark_seq_add_rmsnorm", "llark_seq_rmsnorm_rows",
     "llark_seq_relu2", "llark_linear_rows", "llark_linear_simt", "llark_seq_qk_headnorm", "llark_seq_swa_attn",
     "llark_seq_swa_attn_mma",
     "llark_seq_kv_ring_write", "llark_seq_glr_scan", "llark_seq_glr_combine", "llark_seq_head_rmsnorm",
+    "llark_linear_simt_w32", "llark_seq_group_rmsnorm", "llark_seq_residual_combine", "llark_seq_conv_act",
+    "llark_seq_delta_prep", "llark_seq_delta_scan", "llark_seq_head_norm_gate", "llark_seq_latent_prep",
+    "llark_seq_head_linear", "llark_seq_moe_route", "llark_seq_moe_tile_rows", "llark_seq_moe_sort", "llark_seq_moe_up",
+    "llark_seq_moe_down", "llark_seq_tanh",
 ]
 # what libllark_serve.so (`make serve`: GEMM core + decode linears + the ops above) exports
 SERVE_SYMBOLS = SEQ_SYMBOLS + ["llark_last_cuda_error", "llark_init", "llark_gemm", "llark_gemm_ex", "llark_gemv"]
@@ -150,6 +154,21 @@ def lib():
             "llark_seq_glr_scan": ([P, LL, I, I, I, P, P, P, P, P, P, P, P, P, I, I, I, I, P], I),
             "llark_seq_glr_combine": ([P, P, P, P, P, I, I, I, I, P], I),
             "llark_seq_head_rmsnorm": ([P, P, P, LL, I, F, I, P], I),
+            "llark_linear_simt_w32": ([P, LL, P, LL, P, LL, P, I, I, I, I, P], I),
+            "llark_seq_group_rmsnorm": ([P, P, P, P, P, P, I, I, I, F, I, P], I),
+            "llark_seq_residual_combine": ([P, P, P, P, P, I, P, I, I, P], I),
+            "llark_seq_conv_act": ([P, LL, P, P, P, P, P, P, I, I, I, I, I, P], I),
+            "llark_seq_delta_prep": ([I, P, LL, P, LL, P, LL, P, P, P, LL, P, I, I, I, I, F, P], I),
+            "llark_seq_delta_scan": ([P, P, LL, P, P, P, P, I, I, I, I, P], I),
+            "llark_seq_head_norm_gate": ([P, P, I, P, LL, P, LL, I, I, F, I, P], I),
+            "llark_seq_latent_prep": ([P, LL, P, LL, P, P, I, F, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P], I),
+            "llark_seq_head_linear": ([P, I, LL, I, P, P, LL, I, P, LL, I, I, I, I, I, P], I),
+            "llark_seq_moe_route": ([P, LL, P, P, I, I, I, I, I, F, P], I),
+            "llark_seq_moe_tile_rows": ([], I),
+            "llark_seq_moe_sort": ([P, I, I, P, P, P, P, P], I),
+            "llark_seq_moe_up": ([P, LL, P, I, P, P, P, P, I, I, I, I, P], I),
+            "llark_seq_moe_down": ([P, P, P, P, P, I, I, I, I, P], I),
+            "llark_seq_tanh": ([P, P, LL, I, P], I),
         }
         for name, (argtypes, restype) in sig.items():
             if (os.environ.get("LLARK_LIB_PATH") or subset) and not hasattr(_lib, name):

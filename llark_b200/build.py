@@ -19,7 +19,8 @@ def _sources_newer_than(lib, names):
     return any(os.path.exists(p) and os.path.getmtime(p) > t for p in paths)
 
 
-SERVE_SOURCES = ("gemm_tcgen05.cu", "gemv.cu", "seq_ops.cu", "seq_mixers.cu", "seq_swa_mma.cu", "common.cuh")
+SERVE_SOURCES = ("gemm_tcgen05.cu", "gemv.cu", "seq_ops.cu", "seq_mixers.cu", "seq_swa_mma.cu", "seq_delta.cu",
+                 "seq_latent.cu", "seq_moe.cu", "common.cuh")
 
 
 def ensure_built(verbose=False):

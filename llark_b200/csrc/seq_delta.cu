@@ -1,0 +1,350 @@
+// Delta-rule recurrences of the generation path (layer-list decoders): a matrix state S [D, E] per head and request that
+// every token decays per key channel, corrects along one direction and writes into,
+//
+//     S_t[:, e] = d_t * S_(t-1)[:, e] + p1_t * (z_t . S_(t-1)[:, e]) + p2_t * v_t[e],      o_t[e] = q_t . S_t[:, e]
+//
+// with five D-vectors per token and head. Two rules are stated in that form by llark_seq_delta_prep:
+//
+//   gated delta rule          S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q   (q, k unit vectors, q / sqrt D)
+//                             d = g, z = g k, p1 = -beta k, p2 = beta k          g = exp(-exp(A) softplus(a + dt))
+//   generalized delta rule    S <- diag(w) S - (a u)(u^T S) + k v^T,  u = k / |k|;  o = S^T r
+//                             d = w, z = u, p1 = -(a u), p2 = k                  w = exp(-exp(-1/2) sigmoid(.)), a = sigmoid(.)
+//
+// Everything here is fp32: the state, the vectors, decays, softplus / exponentials, unit norms and the outputs.
+//
+//   llark_seq_conv_act        causal depthwise convolution over a column range of a strided fp32 matrix + SiLU, with
+//                             carry of the last taps-1 inputs per request (and llark_seq_conv_carry, its refresh)
+//   llark_seq_delta_prep      projections -> the five vectors
+//   llark_seq_delta_scan      the recurrence; state read and written once per step
+//   llark_seq_head_norm_gate  per-head RMS norm of o, weight (shared by the heads or one per head), sigmoid gate -> ACT
+#include "common.cuh"
+
+namespace llark {
+extern thread_local int g_last_cuda_error;
+namespace delta {
+
+static int check_launch() {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        g_last_cuda_error = (int)e;
+        return LLARK_ECUDA;
+    }
+    return LLARK_OK;
+}
+
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplusf_(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+// ------------------------------------------------------------------------------------------------ convolution + SiLU
+// out[t, c] = act(sum_j w[c, j] * in[t - taps + 1 + j, c]) with in = src[:, col0 + c]; rows before the step's first come
+// from carry[slot][k][c], k = 0 .. taps-2 oldest first. inline_carry: one token per request, the reading thread shifts.
+__global__ void conv_act_kernel(const float* __restrict__ src, long long ld, const float* __restrict__ w,
+                                float* __restrict__ carry, const int* __restrict__ tok_seq, const int* __restrict__ cu,
+                                const int* __restrict__ slot, float* __restrict__ out, int n_ch, int taps, int silu,
+                                int inline_carry) {
+    const int t = blockIdx.x;
+    const int b = tok_seq[t];
+    const int local = t - cu[b];
+    float* cr = carry + (long long)slot[b] * (taps - 1) * n_ch;
+    for (int c = threadIdx.x; c < n_ch; c += blockDim.x) {
+        const float cur = src[(long long)t * ld + c];
+        float acc = 0.f;
+        for (int j = 0; j < taps - 1; ++j) {
+            const int s = local - taps + 1 + j;
+            const float v = s >= 0 ? src[(long long)(t - local + s) * ld + c] : cr[(long long)(taps - 1 + s) * n_ch + c];
+            acc = fmaf(w[c * taps + j], v, acc);
+        }
+        acc = fmaf(w[c * taps + taps - 1], cur, acc);
+        out[(long long)t * n_ch + c] = silu ? acc * sigmoidf_(acc) : acc;
+        if (inline_carry) {
+            for (int k = 0; k + 1 < taps - 1; ++k) cr[(long long)k * n_ch + c] = cr[(long long)(k + 1) * n_ch + c];
+            if (taps > 1) cr[(long long)(taps - 2) * n_ch + c] = cur;
+        }
+    }
+}
+
+// new carry[k] = input at local index n - (taps-1) + k: a row of this step, or an older carry entry when negative
+__global__ void conv_carry_kernel(const float* __restrict__ src, long long ld, float* __restrict__ carry,
+                                  const int* __restrict__ cu, const int* __restrict__ slot, int n_ch, int taps) {
+    const int b = blockIdx.x;
+    const int r0 = cu[b], n = cu[b + 1] - r0;
+    float* cr = carry + (long long)slot[b] * (taps - 1) * n_ch;
+    for (int c = threadIdx.x; c < n_ch; c += blockDim.x)
+        for (int k = 0; k < taps - 1; ++k) {  // ascending: entry k + n >= k is read before it is rewritten
+            const int s = n - (taps - 1) + k;
+            cr[(long long)k * n_ch + c] = s >= 0 ? src[(long long)(r0 + s) * ld + c] : cr[(long long)(taps - 1 + s) * n_ch + c];
+        }
+}
+
+// ------------------------------------------------------------------------------------------------ the five vectors
+// Warp per (token, head). vec[t][h] = { q, z, d, p1, p2 } each [D].
+//   rule 0 (gated delta):       q, k [n_tok, G, D] (head h reads h / (H / G)); dec [n_tok, H*D] pre-activation of the
+//                               decay, + dec_bias [H*D]; rate_log [H]; mix [n_tok, H] pre-activation of beta
+//   rule 1 (generalized delta): q = r, k [n_tok, H, D]; dec [n_tok, H*D] (bias included); mix [n_tok, H*D] pre-activation
+//                               of the removal rate
+__global__ void delta_prep_kernel(int rule, const float* __restrict__ q, long long q_ld, const float* __restrict__ k,
+                                  long long k_ld, const float* __restrict__ dec, long long dec_ld,
+                                  const float* __restrict__ dec_bias, const float* __restrict__ rate_log,
+                                  const float* __restrict__ mix, long long mix_ld, float* __restrict__ vec, int n_tok,
+                                  int H, int G, int D, float unit_eps) {
+    const int lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (long long)n_tok * H) return;
+    const long long t = item / H;
+    const int h = (int)(item % H);
+    const int g = h / (H / G);
+    const float* qr = q + t * q_ld + (long long)g * D;
+    const float* kr = k + t * k_ld + (long long)g * D;
+    float* o = vec + item * 5 * D;
+    float sk = 0.f, sq = 0.f;
+    for (int d = lane; d < D; d += 32) {
+        sk = fmaf(kr[d], kr[d], sk);
+        sq = fmaf(qr[d], qr[d], sq);
+    }
+    sk = warp_sum(sk);
+    sq = warp_sum(sq);
+    const float rk = 1.0f / sqrtf(sk + unit_eps);
+    if (rule == 0) {
+        const float rq = 1.0f / sqrtf(sq + unit_eps) / sqrtf((float)D);
+        const float beta = sigmoidf_(mix[t * mix_ld + h]);
+        const float rate = expf(rate_log[h]);
+        for (int d = lane; d < D; d += 32) {
+            const float kh = kr[d] * rk;
+            const float gd = expf(-rate * softplusf_(dec[t * dec_ld + (long long)h * D + d] + dec_bias[h * D + d]));
+            o[d] = qr[d] * rq;
+            o[D + d] = kh * gd;
+            o[2 * D + d] = gd;
+            o[3 * D + d] = -beta * kh;
+            o[4 * D + d] = beta * kh;
+        }
+    } else {
+        for (int d = lane; d < D; d += 32) {
+            const float u = kr[d] * rk;
+            const float wd = expf(-0.60653065971263342f * sigmoidf_(dec[t * dec_ld + (long long)h * D + d]));
+            const float a = sigmoidf_(mix[t * mix_ld + (long long)h * D + d]);
+            o[d] = qr[d];
+            o[D + d] = u;
+            o[2 * D + d] = wd;
+            o[3 * D + d] = -(a * u);
+            o[4 * D + d] = kr[d];
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ the recurrence
+// Block per (column slice, head, request). R adjacent lanes share column e of S; lane r owns rows r * DPT .. + DPT - 1 in
+// registers and the partial sums over rows are added by shuffle. The vectors and values of TS tokens are brought to
+// shared memory with cp.async while the previous TS are computed. Rows d >= D are zero padding (DPT * R >= D).
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <int DPT>
+__global__ void __launch_bounds__(256)
+delta_scan_kernel(const float* __restrict__ vec, const float* __restrict__ v, long long v_ld, float* __restrict__ state,
+                  float* __restrict__ o, const int* __restrict__ cu, const int* __restrict__ slot, int H, int D, int E,
+                  int R, int cols, int ts) {
+    extern __shared__ __align__(16) float sm[];
+    const int Dp = DPT * R;
+    const int stage_floats = ts * (5 * Dp + cols);
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int col = threadIdx.x / R, r = threadIdx.x % R;
+    const int e0 = blockIdx.x * cols;
+    const int e = e0 + col;
+    const int row0 = cu[b], n = cu[b + 1] - row0;
+    const bool live = e < E;
+    float S[DPT];
+    float* sp = state + (((long long)slot[b] * H + h) * D) * E;
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+        const int d = r * DPT + i;
+        S[i] = (live && d < D) ? sp[(long long)d * E + e] : 0.f;
+    }
+    for (int i = threadIdx.x; i < 2 * stage_floats; i += blockDim.x) sm[i] = 0.f;  // padding rows stay zero
+    __syncthreads();
+    const bool vec16 = (D % 4) == 0;
+    auto issue = [&](int tok0, int st) {
+        float* base = sm + st * stage_floats;
+        const int cnt = n - tok0 < ts ? n - tok0 : ts;
+        if (vec16) {
+            const int per = 5 * D / 4, dq = D / 4;
+            for (int i = threadIdx.x; i < cnt * per; i += blockDim.x) {
+                const int tk = i / per, rem = i % per, which = rem / dq, d4 = rem % dq;
+                cp_async16(base + (tk * 5 + which) * Dp + d4 * 4,
+                           vec + (((long long)(row0 + tok0 + tk) * H + h) * 5 + which) * D + d4 * 4);
+            }
+        } else {
+            const int per = 5 * D;
+            for (int i = threadIdx.x; i < cnt * per; i += blockDim.x) {
+                const int tk = i / per, rem = i % per, which = rem / D, d = rem % D;
+                cp_async4(base + (tk * 5 + which) * Dp + d,
+                          vec + (((long long)(row0 + tok0 + tk) * H + h) * 5 + which) * D + d);
+            }
+        }
+        float* sv = base + ts * 5 * Dp;
+        for (int i = threadIdx.x; i < cnt * cols; i += blockDim.x) {
+            const int tk = i / cols, c = i % cols;
+            if (e0 + c < E) cp_async4(sv + tk * cols + c, v + (long long)(row0 + tok0 + tk) * v_ld + (long long)h * E + e0 + c);
+        }
+        cp_async_commit();
+    };
+    issue(0, 0);
+    int st = 0;
+    for (int tok0 = 0; tok0 < n; tok0 += ts, st ^= 1) {
+        if (tok0 + ts < n) {
+            issue(tok0 + ts, st ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const float* base = sm + st * stage_floats;
+        const float* sv = base + ts * 5 * Dp;
+        const int cnt = n - tok0 < ts ? n - tok0 : ts;
+        for (int tk = 0; tk < cnt; ++tk) {
+            const float4* pq = reinterpret_cast<const float4*>(base + (tk * 5 + 0) * Dp + r * DPT);
+            const float4* pz = reinterpret_cast<const float4*>(base + (tk * 5 + 1) * Dp + r * DPT);
+            const float4* pd = reinterpret_cast<const float4*>(base + (tk * 5 + 2) * Dp + r * DPT);
+            const float4* p1 = reinterpret_cast<const float4*>(base + (tk * 5 + 3) * Dp + r * DPT);
+            const float4* p2 = reinterpret_cast<const float4*>(base + (tk * 5 + 4) * Dp + r * DPT);
+            float zs = 0.f;
+#pragma unroll
+            for (int i = 0; i < DPT / 4; ++i) {
+                const float4 z = pz[i];
+                zs = fmaf(z.x, S[4 * i], zs);
+                zs = fmaf(z.y, S[4 * i + 1], zs);
+                zs = fmaf(z.z, S[4 * i + 2], zs);
+                zs = fmaf(z.w, S[4 * i + 3], zs);
+            }
+            for (int m = 1; m < R; m <<= 1) zs += __shfl_xor_sync(0xffffffffu, zs, m);
+            const float vv = sv[tk * cols + col];
+            float os = 0.f;
+#pragma unroll
+            for (int i = 0; i < DPT / 4; ++i) {
+                const float4 dd = pd[i], a = p1[i], c = p2[i], qq = pq[i];
+                S[4 * i] = fmaf(c.x, vv, fmaf(a.x, zs, dd.x * S[4 * i]));
+                S[4 * i + 1] = fmaf(c.y, vv, fmaf(a.y, zs, dd.y * S[4 * i + 1]));
+                S[4 * i + 2] = fmaf(c.z, vv, fmaf(a.z, zs, dd.z * S[4 * i + 2]));
+                S[4 * i + 3] = fmaf(c.w, vv, fmaf(a.w, zs, dd.w * S[4 * i + 3]));
+                os = fmaf(qq.x, S[4 * i], os);
+                os = fmaf(qq.y, S[4 * i + 1], os);
+                os = fmaf(qq.z, S[4 * i + 2], os);
+                os = fmaf(qq.w, S[4 * i + 3], os);
+            }
+            for (int m = 1; m < R; m <<= 1) os += __shfl_xor_sync(0xffffffffu, os, m);
+            if (r == 0 && live) o[(long long)(row0 + tok0 + tk) * H * E + (long long)h * E + e] = os;
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+        const int d = r * DPT + i;
+        if (live && d < D) sp[(long long)d * E + e] = S[i];
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ read-out norm + gate
+// Warp per (token, head): y = o / sqrt(mean(o^2) + eps) * w * sigmoid(gate)
+template <typename T>
+__global__ void head_norm_gate_kernel(const float* __restrict__ x, const float* __restrict__ w, int w_per_head,
+                                      const float* __restrict__ gate, long long gate_ld, T* __restrict__ out,
+                                      long long n_items, int H, int E, float eps) {
+    const int lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= n_items) return;
+    const long long t = item / H;
+    const int h = (int)(item % H);
+    const float* xr = x + item * E;
+    float ss = 0.f;
+    for (int e = lane; e < E; e += 32) ss = fmaf(xr[e], xr[e], ss);
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss / (float)E + eps);
+    const float* wr = w + (w_per_head ? (long long)h * E : 0);
+    for (int e = lane; e < E; e += 32) {
+        float y = xr[e] * r * wr[e];
+        if (gate) y *= sigmoidf_(gate[t * gate_ld + (long long)h * E + e]);
+        stf(out + item * E + e, y);
+    }
+}
+
+}  // namespace delta
+}  // namespace llark
+
+using namespace llark;
+using namespace llark::delta;
+
+extern "C" int llark_seq_conv_act(const float* src, long long ld, const float* w, float* carry, const int* tok_seq,
+                                  const int* cu, const int* slot, float* out, int n_tok, int n_seq, int n_ch, int taps,
+                                  int silu, cudaStream_t st) {
+    if (n_tok <= 0 || n_seq <= 0 || n_ch <= 0 || taps < 1 || !src || !w || !out || ld < n_ch || (taps > 1 && !carry) ||
+        !tok_seq || !cu || !slot)
+        return LLARK_EINVAL;
+    int th = 32;
+    while (th < n_ch && th < 256) th <<= 1;
+    const int inline_carry = n_tok == n_seq;  // every request brings one token
+    conv_act_kernel<<<n_tok, th, 0, st>>>(src, ld, w, carry, tok_seq, cu, slot, out, n_ch, taps, silu, inline_carry);
+    int rc = check_launch();
+    if (rc != LLARK_OK || inline_carry || taps == 1) return rc;
+    conv_carry_kernel<<<n_seq, th, 0, st>>>(src, ld, carry, cu, slot, n_ch, taps);
+    return check_launch();
+}
+
+extern "C" int llark_seq_delta_prep(int rule, const float* q, long long q_ld, const float* k, long long k_ld,
+                                    const float* dec, long long dec_ld, const float* dec_bias, const float* rate_log,
+                                    const float* mix, long long mix_ld, float* vec, int n_tok, int H, int G, int D,
+                                    float unit_eps, cudaStream_t st) {
+    if (n_tok <= 0 || H <= 0 || G <= 0 || (H % G) || D <= 0 || !q || !k || !dec || !mix || !vec) return LLARK_EINVAL;
+    if (rule == 0 ? (!dec_bias || !rate_log) : (rule != 1 || G != H)) return LLARK_EINVAL;
+    const long long items = (long long)n_tok * H;
+    delta_prep_kernel<<<(unsigned)((items + 3) / 4), 128, 0, st>>>(rule, q, q_ld, k, k_ld, dec, dec_ld, dec_bias, rate_log,
+                                                                   mix, mix_ld, vec, n_tok, H, G, D, unit_eps);
+    return check_launch();
+}
+
+extern "C" int llark_seq_delta_scan(const float* vec, const float* v, long long v_ld, float* state, float* o,
+                                    const int* cu, const int* slot, int n_seq, int H, int D, int E, cudaStream_t st) {
+    if (n_seq <= 0 || H <= 0 || D <= 0 || E <= 0 || !vec || !v || !state || !o || !cu || !slot) return LLARK_EINVAL;
+    constexpr int DPT = 32;
+    if (D > 8 * DPT) return LLARK_EINVAL;
+    int R = 1;
+    while (R * DPT < D) R <<= 1;
+    // columns per block: enough blocks to fill the GPU at small batches, full warps, at most 256 threads
+    int cols = 256 / R;
+    const int min_cols = 32 / R > 8 ? 32 / R : 8;
+    while (cols > min_cols && (long long)((E + cols - 1) / cols) * H * n_seq < 2 * 148) cols >>= 1;
+    while (cols > min_cols && cols / 2 >= E) cols >>= 1;
+    const int ts = D <= 128 ? 8 : 4;
+    const size_t smem = sizeof(float) * 2 * (size_t)ts * (5 * DPT * R + cols);
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(delta_scan_kernel<DPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+        attr_set = true;
+    }
+    dim3 grid((E + cols - 1) / cols, H, n_seq);
+    delta_scan_kernel<DPT><<<grid, cols * R, smem, st>>>(vec, v, v_ld, state, o, cu, slot, H, D, E, R, cols, ts);
+    return check_launch();
+}
+
+extern "C" int llark_seq_head_norm_gate(const float* x, const float* w, int w_per_head, const float* gate,
+                                        long long gate_ld, void* out, long long n_tok, int H, int E, float eps,
+                                        int act_fp32, cudaStream_t st) {
+    if (n_tok <= 0 || H <= 0 || E <= 0 || !x || !w || !out) return LLARK_EINVAL;
+    const long long items = n_tok * H;
+    const unsigned grid = (unsigned)((items + 3) / 4);
+    if (act_fp32)
+        head_norm_gate_kernel<float><<<grid, 128, 0, st>>>(x, w, w_per_head, gate, gate_ld, (float*)out, items, H, E, eps);
+    else
+        head_norm_gate_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(x, w, w_per_head, gate, gate_ld, (__nv_bfloat16*)out,
+                                                                   items, H, E, eps);
+    return check_launch();
+}

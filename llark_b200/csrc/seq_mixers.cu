@@ -246,7 +246,8 @@ __global__ void kv_ring_write_kernel(const T* __restrict__ kn, const T* __restri
     const long long p = pos0[b] + local;
     const long long e = (long long)slot[b] * cap + (p % cap);
     for (int d = threadIdx.x; d < GD; d += blockDim.x) kring[e * GD + d] = kn[(long long)t * GD + d];
-    for (int d = threadIdx.x; d < GE; d += blockDim.x) vring[e * GE + d] = vv[(long long)t * GE + d];
+    if (vring)  // keys that are their own values keep one ring
+        for (int d = threadIdx.x; d < GE; d += blockDim.x) vring[e * GE + d] = vv[(long long)t * GE + d];
 }
 
 // ------------------------------------------------------------------------------------------------ gated linear recurrence
@@ -476,6 +477,8 @@ static int launch_swa(const void* qn, const void* kn, const void* vv, const void
     else if (dpl <= 2) LLARK_SWA(2);
     else if (dpl <= 4) LLARK_SWA(4);
     else if (dpl <= 8) LLARK_SWA(8);
+    else if (dpl <= 16) LLARK_SWA(16);
+    else if (dpl <= 32) LLARK_SWA(32);
     else return LLARK_EINVAL;
 #undef LLARK_SWA
     return check_launch();
@@ -500,7 +503,7 @@ extern "C" int llark_seq_swa_attn(const void* qn, const void* kn, const void* vv
 extern "C" int llark_seq_kv_ring_write(const void* kn, const void* vv, void* kring, void* vring, const int* tok_seq,
                                        const int* cu, const int* pos0, const int* slot, int n_tok, int GD, int GE, int cap,
                                        int act_fp32, cudaStream_t st) {
-    if (n_tok <= 0 || GD <= 0 || GE <= 0 || cap <= 0 || !kn || !vv || !kring || !vring) return LLARK_EINVAL;
+    if (n_tok <= 0 || GD <= 0 || GE <= 0 || cap <= 0 || !kn || !kring || (vring && !vv)) return LLARK_EINVAL;
     if (act_fp32)
         kv_ring_write_kernel<float><<<n_tok, 128, 0, st>>>((const float*)kn, (const float*)vv, (float*)kring,
                                                            (float*)vring, tok_seq, cu, pos0, slot, GD, GE, cap);

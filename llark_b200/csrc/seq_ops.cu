@@ -297,6 +297,12 @@ __global__ void relu2_kernel(const T* __restrict__ u, T* __restrict__ y, long lo
     }
 }
 
+template <typename T>
+__global__ void tanh_kernel(const float* __restrict__ u, T* __restrict__ y, long long n) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        stf(y + i, tanhf(u[i]));
+}
+
 // ------------------------------------------------------------------------------------------------ linears
 // Few rows (decode): a warp owns NC adjacent output columns, its lanes stride over K in 16-byte pieces (streamed,
 // evict-first), the rows of A come from L1 / L2 and are read once per NC weight pieces.
@@ -360,9 +366,9 @@ linear_rows_kernel(const T* __restrict__ A, long long lda, const T* __restrict__
 }
 
 // Any shape: 64 x 64 tile, 16-deep k slices through shared memory, 4 x 4 outputs per thread, fp32 FMA.
-template <typename T, typename TC>
+template <typename T, typename TC, typename TW = T>
 __global__ void __launch_bounds__(256)
-linear_simt_kernel(const T* __restrict__ A, long long lda, const T* __restrict__ W, long long ldw, TC* __restrict__ Cm,
+linear_simt_kernel(const T* __restrict__ A, long long lda, const TW* __restrict__ W, long long ldw, TC* __restrict__ Cm,
                    long long ldc, const float* __restrict__ bias, int M, int N, int K) {
     constexpr int BM = 64, BN = 64, BK = 16;
     __shared__ float As[BK][BM + 4];
@@ -398,6 +404,49 @@ linear_simt_kernel(const T* __restrict__ A, long long lda, const T* __restrict__
             const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
             if (m < M && n < N) stf(Cm + (long long)m * ldc + n, acc[i][j] + (bias ? bias[n] : 0.f));
         }
+}
+
+// ------------------------------------------------------------------------------------------------ grouped RMS norm
+// Row r of the output is the norm of x[rows ? rows[r] : r] (+ add_vec): the row is cut into `groups` equal consecutive
+// parts, each divided by its own sqrt(mean(part^2) + eps), the whole times w. With x_out the sum x + add_vec is also
+// written (a vector added to the residual stream right before a norm).
+template <typename T>
+__global__ void group_rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                                     const float* __restrict__ add_vec, float* __restrict__ x_out,
+                                     const float* __restrict__ w, T* __restrict__ out, int C, int groups, float eps) {
+    __shared__ float red[32];
+    const long long src = rows ? rows[blockIdx.x] : blockIdx.x;
+    const float* xr = x + src * C;
+    const int per = C / groups;
+    for (int g = 0; g < groups; ++g) {
+        const int c0 = g * per;
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < per; c += blockDim.x) {
+            const float v = xr[c0 + c] + (add_vec ? add_vec[c0 + c] : 0.f);
+            ss = fmaf(v, v, ss);
+        }
+        ss = block_sum(ss, red);
+        const float r = 1.0f / sqrtf(ss / (float)per + eps);
+        for (int c = threadIdx.x; c < per; c += blockDim.x) {
+            const float v = xr[c0 + c] + (add_vec ? add_vec[c0 + c] : 0.f);
+            if (x_out) x_out[src * C + c0 + c] = v;
+            stf(out + (long long)blockIdx.x * C + c0 + c, v * r * w[c0 + c]);
+        }
+    }
+}
+
+// x_out = x + (y + sum_k wts[t, k] * z[pos_of[t * top + k]]): the residual sum of a layer whose sublayers run side by
+// side, the second one a mixture whose chosen experts' outputs sit in rows pos_of[...] of z (top = 0: no second one).
+__global__ void residual_combine_kernel(const float* __restrict__ x, const float* __restrict__ y,
+                                        const float* __restrict__ z, const int* __restrict__ pos_of,
+                                        const float* __restrict__ wts, int top, float* __restrict__ x_out, int C) {
+    const long long t = blockIdx.x;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float m = 0.f;
+        for (int k = 0; k < top; ++k)
+            m = fmaf(wts[t * top + k], z[(long long)pos_of[t * top + k] * C + c], m);
+        x_out[t * C + c] = x[t * C + c] + (y[t * C + c] + m);
+    }
 }
 
 static int norm_threads(int C) {
@@ -558,5 +607,49 @@ extern "C" int llark_linear_simt(const void* A, long long lda, const void* W, lo
     else
         linear_simt_kernel<bf16_t, bf16_t><<<grid, 256, 0, st>>>((const bf16_t*)A, lda, (const bf16_t*)W, ldw, (bf16_t*)C,
                                                                  ldc, bias, M, N, K);
+    return check_launch();
+}
+
+extern "C" int llark_linear_simt_w32(const void* A, long long lda, const float* W, long long ldw, float* C,
+                                     long long ldc, const float* bias, int M, int N, int K, int in_fp32,
+                                     cudaStream_t st) {
+    if (M <= 0 || N <= 0 || K <= 0 || !A || !W || !C || lda < K || ldw < K || ldc < N) return LLARK_EINVAL;
+    dim3 grid((N + 63) / 64, (M + 63) / 64);
+    if (in_fp32)
+        linear_simt_kernel<float, float, float><<<grid, 256, 0, st>>>((const float*)A, lda, W, ldw, C, ldc, bias, M, N, K);
+    else
+        linear_simt_kernel<bf16_t, float, float><<<grid, 256, 0, st>>>((const bf16_t*)A, lda, W, ldw, C, ldc, bias, M, N,
+                                                                      K);
+    return check_launch();
+}
+
+extern "C" int llark_seq_group_rmsnorm(const float* x, const int* rows, const float* add_vec, float* x_out,
+                                       const float* w, void* out, int n_rows, int C, int groups, float eps, int out_fp32,
+                                       cudaStream_t st) {
+    if (n_rows <= 0 || C <= 0 || groups <= 0 || (C % groups) || !x || !w || !out) return LLARK_EINVAL;
+    if (x_out && rows) return LLARK_EINVAL;
+    const int th = norm_threads(C / groups * 4);
+    if (out_fp32)
+        group_rmsnorm_kernel<float><<<n_rows, th, 0, st>>>(x, rows, add_vec, x_out, w, (float*)out, C, groups, eps);
+    else
+        group_rmsnorm_kernel<bf16_t><<<n_rows, th, 0, st>>>(x, rows, add_vec, x_out, w, (bf16_t*)out, C, groups, eps);
+    return check_launch();
+}
+
+extern "C" int llark_seq_residual_combine(const float* x, const float* y, const float* z, const int* pos_of,
+                                          const float* wts, int top, float* x_out, int n_tok, int C, cudaStream_t st) {
+    if (n_tok <= 0 || C <= 0 || top < 0 || !x || !y || !x_out || (top > 0 && (!z || !pos_of || !wts)))
+        return LLARK_EINVAL;
+    residual_combine_kernel<<<n_tok, norm_threads(C * 4), 0, st>>>(x, y, z, pos_of, wts, top, x_out, C);
+    return check_launch();
+}
+
+extern "C" int llark_seq_tanh(const float* u, void* y, long long n, int act_fp32, cudaStream_t st) {
+    if (n <= 0 || !u || !y) return LLARK_EINVAL;
+    const unsigned grid = (unsigned)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    if (act_fp32)
+        tanh_kernel<float><<<grid, 256, 0, st>>>(u, (float*)y, n);
+    else
+        tanh_kernel<bf16_t><<<grid, 256, 0, st>>>(u, (bf16_t*)y, n);
     return check_launch();
 }

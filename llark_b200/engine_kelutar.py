@@ -8,9 +8,8 @@ with the mixer chosen per layer from llark_b200.mixers.MIXERS ("attention", "hgr
 added to the scaled token embedding, a final RMS norm and an untied head. A layer may name another layer whose weights
 it reuses; its state is its own.
 
-The engine is host-side orchestration only, like LlamaEngine: every FLOP is a C-ABI call. One `step()` runs a PACKED
-batch (llark_b200.state_cache): requests that start, go on by a portion of their prompt or decode one token are the
-same kernels with other numbers, so there is one step function for prefill and decode. Precision: the residual stream,
+The step function is llark_b200.engine_seq.LayerListEngine.step (one function for prefill and decode of a packed batch);
+this class states what Kelutar's layers do. Precision: the residual stream,
 norms, attention scores and softmax, gates and the recurrent state are fp32 in both modes; matrix products and the
 activations between them are bf16 with fp32 accumulation (dtype=torch.bfloat16, the serving mode: tcgen05 GEMM core for
 prefill, weight-streaming linears for decode) or true fp32 (dtype=torch.float32: SIMT linears, no TF32).
@@ -18,21 +17,19 @@ prefill, weight-streaming linears for decode) or true fp32 (dtype=torch.float32:
 import torch
 
 from . import ops
+from .engine_seq import LayerListEngine
 from .mixers import FEED_FORWARDS, MIXERS
 from .state_cache import StateCache
 
 F32 = torch.float32
 
 
-class KelutarEngine:
+class KelutarEngine(LayerListEngine):
     def __init__(self, config, weights, device, dtype=torch.bfloat16):
         """config: llark_b200.models.kelutar.KelutarConfig; weights: name -> tensor (any device / float dtype)."""
-        dev = torch.device(device)
-        if dev.type != "cuda":
-            raise RuntimeError("llark_b200 has no CPU path: the engine needs a CUDA device (B200)")
-        if dtype not in (torch.bfloat16, torch.float32):
-            raise TypeError("dtype must be torch.bfloat16 or torch.float32")
-        self.cfg, self.device, self.act = config, dev, dtype
+        dev = self._init_device(device, dtype)
+        self.cfg = config
+        self.max_positions = config.max_positions
         C = config.width
         self.embed = weights["embed"].to(device=dev, dtype=dtype).contiguous()
         self.pos = weights["pos"].to(device=dev, dtype=dtype).contiguous()
@@ -78,31 +75,12 @@ class KelutarEngine:
         cache.layers = layers
         return cache
 
-    # ------------------------------------------------------------------------------------------ one step
-    @torch.no_grad()
-    def step(self, cache, slots, tokens, want=None, return_residuals=False):
-        """slots: the requests of this step; tokens[b]: the next token ids of request slots[b] (they continue at the
-        position where the request stopped); want[b]: indices into tokens[b] whose logits are asked for (None: the last
-        one of each). Returns fp32 logits [n_wanted, vocab] in the order of the requests and of `want` (None when nothing
-        is wanted). The caches advance by the step's tokens."""
+    # ------------------------------------------------------------------------------------------ one step (hooks)
+    def _embed(self, ids, st):
+        return ops.seq_embed(ids, st, self.embed, self.pos, self.cfg.embedding_scale)
+
+    def _run_layers(self, cache, x, st, residuals):
         cfg = self.cfg
-        lens = [len(t) for t in tokens]
-        st = cache.layout(slots, lens)
-        for s, n in zip(slots, lens):
-            if cache.length[s] + n > cfg.max_positions:
-                raise ValueError("a request grows past max_positions")
-        flat = [int(t) for ts in tokens for t in ts]
-        if flat and (min(flat) < 0 or max(flat) >= cfg.vocab):
-            raise ValueError("token id outside the vocabulary")
-        ids = torch.tensor(flat, dtype=torch.int32).to(self.device, non_blocking=True)
-        if want is None:
-            want = [[n - 1] for n in lens]
-        rows = [st.cu_host[b] + int(k) for b, w in enumerate(want) for k in w]
-        for b, w in enumerate(want):
-            if any(k < 0 or k >= lens[b] for k in w):
-                raise ValueError("a wanted place lies outside the request's tokens")
-        x = ops.seq_embed(ids, st, self.embed, self.pos, cfg.embedding_scale)
-        residuals = []
         for entry in cache.layers:
             pk = entry["pk"]
             hc = ops.seq_short_conv(x, pk["canon"], cache.view(entry["tail"]), st, self.act)
@@ -112,14 +90,10 @@ class KelutarEngine:
             else:
                 x, xa = ops.seq_add_rmsnorm(x, y, pk["norm1"], cfg.eps, act=self.act)
                 x = ops.seq_add_rmsnorm(x, entry["ff"].forward(xa), pk["norm2"], cfg.eps)
-            if return_residuals:
+            if residuals is not None:
                 residuals.append(x)
-        cache.advance(slots, lens)
-        logits = None
-        if rows:
-            idx = torch.tensor(rows, dtype=torch.int32).to(self.device, non_blocking=True)
-            hn = ops.seq_rmsnorm_rows(x, idx, self.final_norm, cfg.eps, self.act)
-            logits = ops.linear(hn, self.head, out_dtype=F32)
-        if return_residuals:
-            return logits, residuals
-        return logits
+        return x
+
+    def _logits(self, x, rows):
+        hn = ops.seq_rmsnorm_rows(x, rows, self.final_norm, self.cfg.eps, self.act)
+        return ops.linear(hn, self.head, out_dtype=F32)

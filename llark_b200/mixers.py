@@ -9,7 +9,17 @@ the same packed weights and stores of its own.
     "hgrn2"      GatedLinearRecurrence  HGRN2: S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T silu(q)_t, forget
                                         gate with a learned lower bound, per-head RMS norm of o
     "dense"      ReluSquaredFF          down(relu(up x)^2)
+    "latent_attention"  LatentWindowAttention   keys and values of all heads expanded from one low-rank latent per token plus
+                                        one rotated key part shared by the heads (interleaved rotary pairs, optional
+                                        YaRN blend of the frequencies); only the latent and that part are cached, the
+                                        expansions are folded into the query and the output; sliding window, sigmoid gate
+    "channel_delta"     GatedDeltaRule  S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q with a decay per head and
+                                        key channel, unit q / k behind a short convolution + SiLU, gated per-head RMS norm
+    "general_delta"     GeneralizedDeltaRule    S <- diag(w) S - (a u)(u^T S) + k v^T, u the unit key; o = S^T r
+    "moe"        RoutedExperts          sigmoid router, group-limited top-k, weighted sum of small SwiGLU experts
 """
+import math
+
 import torch
 
 from . import ops
@@ -127,5 +137,215 @@ class ReluSquaredFF:
         return ops.linear(ops.seq_relu2(u), self.w.w_down, out_dtype=F32)
 
 
-MIXERS = {"attention": GatedWindowAttention, "hgrn2": GatedLinearRecurrence}
-FEED_FORWARDS = {"dense": ReluSquaredFF}
+def _expect(pfx, pairs):
+    for t, shape in pairs:
+        if tuple(t.shape) != tuple(shape):
+            raise ValueError(f"{pfx}: tensor of shape {tuple(t.shape)}, expected {tuple(shape)}")
+
+
+def rotary_frequencies(dims, base, scaling=None):
+    """f_i = base^(-2i/dims), i < dims/2 (float64), blended the YaRN way when `scaling` = {factor, original, fast, slow}
+    is given: with where(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(where(fast)), 0),
+    hi = min(ceil(where(slow)), dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) the frequency is
+    f_i / factor * ramp_i + f_i (1 - ramp_i); cos and sin are then multiplied by 0.1 ln(factor) + 1. Returns
+    (frequencies as a float64 tensor, that multiplier)."""
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    f = float(base) ** (-2.0 * i / dims)
+    if not scaling:
+        return f, 1.0
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+
+    def where(turns):
+        return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(float(base)))
+
+    lo = max(math.floor(where(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(where(float(scaling["slow"]))), dims - 1)
+    ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return f / factor * ramp + f * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
+
+
+class LatentWindowAttentionWeights:
+    def __init__(self, w, pfx, spec, width, dev, act):
+        H, Dn, P, E, R = (int(spec[k]) for k in ("heads", "dim", "rot_dim", "vdim", "kv_rank"))
+        self.H, self.Dn, self.P, self.E, self.R = H, Dn, P, E, R
+        self.window = int(spec["mask"]["size"])
+        rot = spec.get("rot") or {}
+        n_rot = int(rot.get("dims", P))
+        if n_rot % 2 or n_rot > P:
+            raise ValueError(f"{pfx}: rot.dims must be even and at most rot_dim")
+        if n_rot:
+            f, self.mult = rotary_frequencies(n_rot, rot["base"], rot.get("scaling"))
+            self.freqs = f.to(device=dev, dtype=F32).contiguous()
+        else:
+            self.freqs, self.mult = None, 1.0
+        # one projection for q | latent + shared rotated key part | gate
+        self.w_in = torch.cat([_mat(w, pfx + "q", dev, act), _mat(w, pfx + "dkv", dev, act), _mat(w, pfx + "g", dev, act)])
+        self.q_n, self.lat_off, self.g_off = H * (Dn + P), H * (Dn + P), H * (Dn + P) + R + P
+        self.norm = _vec(w, pfx + "dkv.norm", dev)
+        uk, uv = _mat(w, pfx + "uk", dev, act), _mat(w, pfx + "uv", dev, act)
+        _expect(pfx, ((self.w_in, (H * (Dn + P) + R + P + H * E, width)), (uk, (H * Dn, R)), (uv, (H * E, R)),
+                      (self.norm, (R,))))
+        self.uk_t = uk.view(H, Dn, R).transpose(1, 2).contiguous()  # [H, R, Dn]: folds W_uk into the query
+        self.uv = uv.view(H, E, R).contiguous()                     # [H, E, R]: unfolds the latent-space output
+        self.scale_h = torch.full((H,), float(spec["scale"]), device=dev, dtype=F32)
+        self.w_o = _mat(w, pfx + "o", dev, act)
+        _expect(pfx, ((self.w_o, (width, H * E)),))
+
+
+class LatentWindowAttention:
+    Weights = LatentWindowAttentionWeights
+
+    def __init__(self, weights, cache, eps, act, max_positions=None):
+        self.w, self.eps, self.act = weights, float(eps), act
+        w = weights
+        self.cap = max(1, min(w.window, int(max_positions))) if max_positions else max(1, w.window)
+        self.h_ring = cache.add_store((self.cap, w.R + w.P), act, zero_on_alloc=False)
+
+    def forward(self, hc, st, cache):
+        w = self.w
+        W = w.R + w.P
+        ring = cache.view(self.h_ring)
+        pin = ops.linear(hc, w.w_in, out_dtype=F32)
+        q, lat, gate = pin[:, :w.q_n], pin[:, w.lat_off:w.g_off], pin[:, w.g_off:]
+        single = st.max_len == 1
+        ckr, qf = ops.seq_latent_prep(q, lat, w.norm, w.freqs, w.mult, st, w.H, w.Dn, w.P, w.R, self.eps, self.act,
+                                      ring=ring if single else None, cap=self.cap)
+        ops.seq_head_linear(q, w.Dn + w.P, w.uk_t, qf, W, N=w.R, K=w.Dn)
+        # one shared key head whose rows [latent | rotated part] are also the values; output columns >= R are unused
+        o = ops.seq_swa_attn(qf, ckr, ckr, ring, ring, None, 0, w.scale_h, st, w.H, 1, W, W, w.window, self.cap,
+                             from_ring_only=single)
+        if not single:
+            ops.seq_kv_ring_write(ckr, None, ring, None, st, self.cap)
+        og = torch.empty((st.n_tok, w.H * w.E), device=hc.device, dtype=self.act)
+        ops.seq_head_linear(o, W, w.uv, og, w.E, N=w.E, K=w.R, gate=gate)
+        return ops.linear(og, w.w_o, out_dtype=F32)
+
+
+class GatedDeltaRuleWeights:
+    def __init__(self, w, pfx, spec, width, dev, act):
+        H, D = int(spec["heads"]), int(spec["dim"])
+        G, E = int(spec.get("kv_heads", H)), int(spec.get("vdim", D))
+        if H % G:
+            raise ValueError("heads must be a multiple of kv_heads")
+        self.H, self.G, self.D, self.E = H, G, D, E
+        a1, g1 = _mat(w, pfx + "a1", dev, act), _mat(w, pfx + "g1", dev, act)
+        self.ra, self.rg = a1.shape[0], g1.shape[0]
+        # one projection for q | k | v | beta, one for the two low-rank bottlenecks
+        self.w_in = torch.cat([_mat(w, pfx + "q", dev, act), _mat(w, pfx + "k", dev, act), _mat(w, pfx + "v", dev, act),
+                               _mat(w, pfx + "b", dev, act)])
+        self.w_low = torch.cat([a1, g1])
+        self.n_conv, self.b_off = 2 * G * D + H * E, 2 * G * D + H * E
+        self.conv = torch.cat([_vec(w, pfx + "q.conv", dev), _vec(w, pfx + "k.conv", dev), _vec(w, pfx + "v.conv", dev)])
+        self.taps = self.conv.shape[1]
+        if "conv" in spec and int(spec["conv"]) != self.taps:
+            raise ValueError(f"{pfx}: convolution tensors do not fit conv = {spec['conv']}")
+        self.a2, self.g2 = _mat(w, pfx + "a2", dev, act), _mat(w, pfx + "g2", dev, act)
+        self.dt_bias, self.rate_log = _vec(w, pfx + "dt_bias", dev), _vec(w, pfx + "A_log", dev)
+        self.norm = _vec(w, pfx + "norm", dev)
+        self.w_o = _mat(w, pfx + "o", dev, act)
+        _expect(pfx, ((self.w_in, (self.n_conv + H, width)), (self.w_low, (self.ra + self.rg, width)),
+                      (self.conv, (self.n_conv, self.taps)), (self.a2, (H * D, self.ra)), (self.g2, (H * E, self.rg)),
+                      (self.dt_bias, (H * D,)), (self.rate_log, (H,)), (self.norm, (E,)), (self.w_o, (width, H * E))))
+
+
+class GatedDeltaRule:
+    Weights = GatedDeltaRuleWeights
+
+    def __init__(self, weights, cache, eps, act, max_positions=None):
+        self.w, self.eps, self.act = weights, float(eps), act
+        w = weights
+        self.h_state = cache.add_store((w.H, w.D, w.E), F32, zero_on_alloc=True)
+        self.h_carry = cache.add_store((max(w.taps - 1, 1), w.n_conv), F32, zero_on_alloc=True)
+
+    def forward(self, hc, st, cache):
+        w = self.w
+        GD = w.G * w.D
+        pin = ops.linear(hc, w.w_in, out_dtype=F32)
+        low = ops.linear(hc, w.w_low, out_dtype=self.act)
+        dec = ops.linear(low[:, :w.ra], w.a2, out_dtype=F32)
+        gate = ops.linear(low[:, w.ra:], w.g2, out_dtype=F32)
+        cv = ops.seq_conv_act(pin[:, :w.n_conv], w.conv, cache.view(self.h_carry), st, silu=True)
+        vec = ops.seq_delta_prep(ops.DELTA_GATED, cv[:, :GD], cv[:, GD:2 * GD], dec, pin[:, w.b_off:], w.H, w.G, w.D,
+                                 dec_bias=w.dt_bias, rate_log=w.rate_log)
+        o = ops.seq_delta_scan(vec, cv[:, 2 * GD:], cache.view(self.h_state), st, w.H, w.D, w.E)
+        on = ops.seq_head_norm_gate(o, w.norm, w.H, w.E, self.eps, self.act, gate=gate)
+        return ops.linear(on, w.w_o, out_dtype=F32)
+
+
+class GeneralizedDeltaRuleWeights:
+    def __init__(self, w, pfx, spec, width, dev, act):
+        H, D = int(spec["heads"]), int(spec["dim"])
+        self.H, self.D = H, D
+        HD = H * D
+        # one projection for r | k | v | removal rate | gate; the rate has a bias
+        self.w_in = torch.cat([_mat(w, pfx + n, dev, act) for n in ("r", "k", "v", "a", "g")])
+        zero = torch.zeros(HD, device=dev, dtype=F32)
+        self.b_in = torch.cat([zero, zero, zero, _vec(w, pfx + "a.b", dev), zero])
+        self.w1, self.w2, self.w0 = _mat(w, pfx + "w1", dev, act), _mat(w, pfx + "w2", dev, act), _vec(w, pfx + "w0", dev)
+        self.norm = _vec(w, pfx + "norm", dev)
+        self.w_o = _mat(w, pfx + "o", dev, act)
+        rw = self.w1.shape[0]
+        _expect(pfx, ((self.w_in, (5 * HD, width)), (self.b_in, (5 * HD,)), (self.w1, (rw, width)), (self.w2, (HD, rw)),
+                      (self.w0, (HD,)), (self.norm, (HD,)), (self.w_o, (width, HD))))
+
+
+class GeneralizedDeltaRule:
+    Weights = GeneralizedDeltaRuleWeights
+
+    def __init__(self, weights, cache, eps, act, max_positions=None):
+        self.w, self.eps, self.act = weights, float(eps), act
+        self.h_state = cache.add_store((weights.H, weights.D, weights.D), F32, zero_on_alloc=True)
+
+    def forward(self, hc, st, cache):
+        w = self.w
+        HD = w.H * w.D
+        pin = ops.linear(hc, w.w_in, bias=w.b_in, out_dtype=F32)
+        low = ops.seq_tanh(ops.linear(hc, w.w1, out_dtype=F32), self.act)
+        dec = ops.linear(low, w.w2, bias=w.w0, out_dtype=F32)
+        vec = ops.seq_delta_prep(ops.DELTA_GENERALIZED, pin[:, :HD], pin[:, HD:2 * HD], dec, pin[:, 3 * HD:4 * HD], w.H,
+                                 w.H, w.D)
+        o = ops.seq_delta_scan(vec, pin[:, 2 * HD:3 * HD], cache.view(self.h_state), st, w.H, w.D, w.D)
+        on = ops.seq_head_norm_gate(o, w.norm, w.H, w.D, self.eps, self.act, gate=pin[:, 4 * HD:], w_per_head=True)
+        return ops.linear(on, w.w_o, out_dtype=F32)
+
+
+class RoutedExpertsWeights:
+    def __init__(self, w, pfx, spec, width, dev, act):
+        r = spec["router"]
+        self.n, self.top = int(r["experts"]), int(r["top"])
+        groups = r.get("groups") or {"count": 1, "keep": 1}
+        self.n_groups, self.keep, self.scale = int(groups["count"]), int(groups["keep"]), float(r.get("scale", 1.0))
+        ff = int(spec["expert"]["ff"])
+        self.ff = ff
+        if self.n % self.n_groups or not 0 < self.keep <= self.n_groups or self.top > self.keep * (self.n // self.n_groups):
+            raise ValueError(f"{pfx}: router groups do not fit experts / top")
+        self.router = _vec(w, pfx + "router", dev)  # the router runs in fp32 whatever the serving dtype
+        self.w_gate_up = torch.stack([torch.cat([_mat(w, f"{pfx}e{e}.gate", dev, act), _mat(w, f"{pfx}e{e}.up", dev, act)])
+                                      for e in range(self.n)]).contiguous()
+        self.w_down = torch.stack([_mat(w, f"{pfx}e{e}.down", dev, act) for e in range(self.n)]).contiguous()
+        _expect(pfx, ((self.router, (self.n, width)), (self.w_gate_up, (self.n, 2 * ff, width)),
+                      (self.w_down, (self.n, width, ff))))
+
+
+class RoutedExperts:
+    """Feed-forward whose result is added to the residual together with the mixer's (side-by-side sublayers)."""
+    Weights = RoutedExpertsWeights
+
+    def __init__(self, weights, act):
+        self.w, self.act = weights, act
+
+    def route(self, x_act):
+        w = self.w
+        return ops.seq_moe_route(ops.linear_w32(x_act, w.router), w.n_groups, w.keep, w.top, w.scale)
+
+    def residual(self, x, y, x_act):
+        """x + (y + experts(x_act)): fp32 residual sum with the mixer's output y."""
+        w = self.w
+        ids, wts = self.route(x_act)
+        z, pos_of = ops.seq_moe_experts(x_act, ids, w.w_gate_up, w.w_down)
+        return ops.seq_residual_combine(x, y, z, pos_of, wts, w.top)
+
+
+MIXERS = {"attention": GatedWindowAttention, "hgrn2": GatedLinearRecurrence, "latent_attention": LatentWindowAttention,
+          "channel_delta": GatedDeltaRule, "general_delta": GeneralizedDeltaRule}
+FEED_FORWARDS = {"dense": ReluSquaredFF, "moe": RoutedExperts}

@@ -10,12 +10,10 @@ with type ("hgrn2" | "attention"), mixer {heads, dim, vdim, kv_heads, mask.size,
 weights_of (optional). Tensor names: embed, pos, final.norm, head, l<i>.norm1, l<i>.norm2, l<i>.canon1, l<i>.mix.*
 (hgrn2: q, f, f.b, lower, v, norm, o; attention: q, q.b, k, k.b, q.norm, k.norm, temp, g, o), l<i>.mlp.up / down.
 """
-import json
-import os
 from dataclasses import dataclass, field
 from typing import List, Optional
 
-import torch
+from llark_b200.models.native import NativeCausalLM
 
 ARCHITECTURE = "Kelutar"
 
@@ -79,59 +77,12 @@ class KelutarConfig:
                 "norm": {"eps": self.eps}, "canon": {"taps": self.taps}, "layers": layers}
 
 
-class KelutarForCausalLM(torch.nn.Module):
-    """Inference-only model object: configuration + engine. `generate` has the call shape of the Llama wrapper's."""
+class KelutarForCausalLM(NativeCausalLM):
+    """Inference-only model object: configuration + engine (llark_b200.models.native.NativeCausalLM)."""
+    config_class = KelutarConfig
 
-    def __init__(self, config: KelutarConfig, weights, device="cuda:0", dtype=torch.bfloat16):
-        super().__init__()
+    @staticmethod
+    def engine_class():
         from llark_b200.engine_kelutar import KelutarEngine
 
-        self.config = config
-        self.generation_config = None
-        self.engine = KelutarEngine(config, weights, device, dtype)
-        self.device_, self.dtype_ = torch.device(device), dtype
-
-    @classmethod
-    def from_pretrained(cls, folder, dtype=torch.bfloat16, device="cuda:0"):
-        from llark_b200.safetensors_io import load_file
-
-        with open(os.path.join(folder, "config.json"), "r", encoding="utf-8") as f:
-            config = KelutarConfig.from_dict(json.load(f))
-        weights = load_file(os.path.join(folder, "model.safetensors"))
-        return cls(config, weights, device=device, dtype=dtype)
-
-    def new_cache(self, n_slots=4):
-        return self.engine.new_cache(n_slots=n_slots)
-
-    @torch.no_grad()
-    def forward(self, input_ids):
-        """Logits fp32 [B, T, vocab] of whole prompts (fresh slots, released afterwards)."""
-        ids = input_ids.tolist()
-        cache = self.new_cache(n_slots=max(len(ids), 1))
-        slots = [cache.alloc() for _ in ids]
-        logits = self.engine.step(cache, slots, ids, want=[list(range(len(r))) for r in ids])
-        return logits.view(len(ids), len(ids[0]), -1)
-
-    @torch.no_grad()
-    def generate(self, inputs=None, input_ids=None, stopping_criteria=None, max_new_tokens=None, max_length=None,
-                 do_sample=None, num_beams=None, eos_token_id=None, pad_token_id=None, **kwargs):
-        """Greedy decoding of a batch of equal-length prompts [B, T] -> [B, T + new] through the framework's
-        generate_with_model: the prompts are prefilled into fresh slots of a StateCache in one packed step, every
-        further token of every row is one decode step."""
-        from llark_b200.generate import generate_with_model
-
-        state = {"cache": None, "slots": None}
-
-        def step_logits(ids):
-            if state["cache"] is None:
-                state["cache"] = self.new_cache(n_slots=max(ids.shape[0], 1))
-                state["slots"] = [state["cache"].alloc() for _ in range(ids.shape[0])]
-                toks = ids.tolist()
-            else:
-                toks = ids[:, -1:].tolist()
-            return self.engine.step(state["cache"], state["slots"], toks)
-
-        return generate_with_model(self, step_logits, inputs=inputs, input_ids=input_ids,
-                                   stopping_criteria=stopping_criteria, max_new_tokens=max_new_tokens,
-                                   max_length=max_length, do_sample=do_sample, num_beams=num_beams,
-                                   eos_token_id=eos_token_id, pad_token_id=pad_token_id)
+        return KelutarEngine

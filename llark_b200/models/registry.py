@@ -19,6 +19,7 @@ def register_native(architecture, module, class_name):
 
 
 register_native("Kelutar", "llark_b200.models.kelutar", "KelutarForCausalLM")
+register_native("Golavik", "llark_b200.models.golavik", "GolavikForCausalLM")
 
 
 def read_config(folder):

@@ -600,8 +600,10 @@ def seq_swa_attn(qn, kn, vv, kring, vring, gate, gate_ld, scale_h, st, H, G, D, 
 
 
 def seq_kv_ring_write(kn, vv, kring, vring, st, cap):
+    """Rows of this step into the rings; vv = vring = None when the keys are their own values (one ring)."""
     check(lib().llark_seq_kv_ring_write(_p(kn), _p(vv), _p(kring), _p(vring), _p(st.tok_seq), _p(st.cu), _p(st.pos0),
-                                        _p(st.slot), st.n_tok, kn.shape[1], vv.shape[1], cap, _actf(kn.dtype), _stream()),
+                                        _p(st.slot), st.n_tok, kn.shape[1], vv.shape[1] if vv is not None else 1, cap,
+                                        _actf(kn.dtype), _stream()),
           "seq_kv_ring_write")
 
 
@@ -642,3 +644,149 @@ def seq_head_rmsnorm(x, w, E, eps, act):
     check(lib().llark_seq_head_rmsnorm(_p(x), _p(w), _p(out), x.numel() // E, E, float(eps), _actf(act), _stream()),
           "seq_head_rmsnorm")
     return out
+
+
+# ------------------------------------------------------------------------------------------------ further parts of
+# layer-list decoders: grouped RMS norm, the residual of side-by-side sublayers, delta-rule recurrences
+# (csrc/seq_delta.cu), latent attention (csrc/seq_latent.cu), routed mixture of experts (csrc/seq_moe.cu)
+def linear_w32(a, w, bias=None):
+    """a [M, K] (bf16 or fp32) @ w fp32 [N, K]^T -> fp32 [M, N]: fp32 arithmetic on 32-bit weights (router logits)."""
+    _req(a), _req(w, torch.float32)
+    M, K = a.shape
+    N = w.shape[0]
+    out = torch.empty((M, N), device=a.device, dtype=torch.float32)
+    check(lib().llark_linear_simt_w32(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), _p(bias), M, N, K,
+                                      _actf(a.dtype), _stream()), "linear_simt_w32")
+    return out
+
+
+def seq_group_rmsnorm(x, w, groups, eps, out_dtype=torch.float32, rows=None, add_vec=None):
+    """RMS norm of fp32 rows in `groups` equal consecutive parts, times w. rows: int32 row numbers to norm (all when
+    None). add_vec fp32 [C]: added to x first; then (x + add_vec, norm) is returned."""
+    _req(x, torch.float32), _req(w, torch.float32)
+    C = x.shape[1]
+    n = rows.numel() if rows is not None else x.shape[0]
+    out = torch.empty((n, C), device=x.device, dtype=out_dtype)
+    x_out = torch.empty_like(x) if add_vec is not None else None
+    check(lib().llark_seq_group_rmsnorm(_p(x), _p(rows), _p(add_vec), _p(x_out), _p(w), _p(out), n, C, int(groups),
+                                        float(eps), _actf(out_dtype), _stream()), "seq_group_rmsnorm")
+    return (x_out, out) if add_vec is not None else out
+
+
+def seq_residual_combine(x, y, z=None, pos_of=None, wts=None, top=0):
+    """x + (y + sum_k wts[t, k] * z[pos_of[t, k]]) fp32 (top = 0: x + y)."""
+    _req(x, torch.float32), _req(y, torch.float32)
+    out = torch.empty_like(x)
+    check(lib().llark_seq_residual_combine(_p(x), _p(y), _p(z), _p(pos_of), _p(wts), int(top), _p(out), x.shape[0],
+                                           x.shape[1], _stream()), "seq_residual_combine")
+    return out
+
+
+def seq_conv_act(src, w, carry, st, silu=True):
+    """src fp32 [n_tok, n_ch] (a column slice of a wider matrix is fine), w fp32 [n_ch, taps], carry fp32
+    [slots, taps-1, n_ch] (updated) -> fp32 [n_tok, n_ch] = act(causal depthwise conv)."""
+    _req(src, torch.float32), _req(w, torch.float32)
+    n_ch, taps = w.shape
+    out = torch.empty((st.n_tok, n_ch), device=src.device, dtype=torch.float32)
+    check(lib().llark_seq_conv_act(_p(src), src.stride(0), _p(w), _p(carry), _p(st.tok_seq), _p(st.cu), _p(st.slot),
+                                   _p(out), st.n_tok, st.n_seq, n_ch, taps, int(silu), _stream()), "seq_conv_act")
+    return out
+
+
+DELTA_GATED, DELTA_GENERALIZED = 0, 1
+
+
+def seq_delta_prep(rule, q, k, dec, mix, H, G, D, dec_bias=None, rate_log=None, unit_eps=1e-6):
+    """The five vectors [n_tok, H, 5, D] of seq_delta_scan from fp32 projections (column slices are fine)."""
+    n = q.shape[0]
+    vec = torch.empty((n, H, 5, D), device=q.device, dtype=torch.float32)
+    check(lib().llark_seq_delta_prep(int(rule), _p(_req(q, torch.float32)), q.stride(0), _p(_req(k, torch.float32)),
+                                     k.stride(0), _p(_req(dec, torch.float32)), dec.stride(0), _p(dec_bias),
+                                     _p(rate_log), _p(_req(mix, torch.float32)), mix.stride(0), _p(vec), n, H, G, D,
+                                     float(unit_eps), _stream()), "seq_delta_prep")
+    return vec
+
+
+def seq_delta_scan(vec, v, state, st, H, D, E):
+    """vec fp32 [n_tok, H, 5, D], v fp32 [n_tok, H*E] (column slice fine), state fp32 [slots, H, D, E] (updated) ->
+    o fp32 [n_tok, H*E]."""
+    _req(vec, torch.float32), _req(v, torch.float32), _req(state, torch.float32)
+    o = torch.empty((st.n_tok, H * E), device=v.device, dtype=torch.float32)
+    check(lib().llark_seq_delta_scan(_p(vec), _p(v), v.stride(0), _p(state), _p(o), _p(st.cu), _p(st.slot), st.n_seq, H,
+                                     D, E, _stream()), "seq_delta_scan")
+    return o
+
+
+def seq_head_norm_gate(x, w, H, E, eps, act, gate=None, w_per_head=False):
+    """x fp32 [n_tok, H*E]: per-head RMS norm, times w ([E] or [H*E]), times sigmoid(gate fp32 [n_tok, H*E]) -> act."""
+    _req(x, torch.float32), _req(w, torch.float32)
+    out = torch.empty(x.shape, device=x.device, dtype=act)
+    check(lib().llark_seq_head_norm_gate(_p(x), _p(w), int(w_per_head), _p(gate), gate.stride(0) if gate is not None else 0,
+                                         _p(out), x.shape[0], H, E, float(eps), _actf(act), _stream()),
+          "seq_head_norm_gate")
+    return out
+
+
+def seq_latent_prep(q, lat, norm_w, freqs, mult, st, H, Dn, P, R, eps, act, ring=None, cap=0):
+    """q fp32 [n_tok, H*(Dn+P)], lat fp32 [n_tok, R+P] (column slices fine) -> ckr act [n_tok, R+P] (normed latent |
+    rotated shared key part) and qf act [n_tok, H, R+P] with columns R.. = rotated query parts (columns < R are left
+    for seq_head_linear). With `ring` the ckr rows also go to the ring entries of the tokens' positions."""
+    n = st.n_tok
+    ckr = torch.empty((n, R + P), device=q.device, dtype=act)
+    qf = torch.empty((n, H * (R + P)), device=q.device, dtype=act)
+    n_rot = 2 * freqs.numel() if freqs is not None else 0
+    check(lib().llark_seq_latent_prep(_p(_req(q, torch.float32)), q.stride(0), _p(_req(lat, torch.float32)),
+                                      lat.stride(0), _p(norm_w), _p(freqs), n_rot, float(mult), _p(ckr), _p(qf), _p(ring),
+                                      _p(st.tok_seq), _p(st.cu), _p(st.pos0), _p(st.slot), n, H, Dn, P, R, int(cap),
+                                      float(eps), _actf(act), _stream()), "seq_latent_prep")
+    return ckr, qf
+
+
+def seq_head_linear(x, x_hs, w, y, y_hs, N, K, gate=None):
+    """y[m, h*y_hs + n] = sum_k x[m, h*x_hs + k] * w[h, n, k] (* sigmoid(gate[m, h*N + n])); x fp32 or the dtype of w;
+    y (given, written in place) has the dtype of w."""
+    H = w.shape[0]
+    check(lib().llark_seq_head_linear(_p(x), int(x.dtype == torch.float32), x.stride(0), x_hs, _p(w), _p(y), y.stride(0),
+                                      y_hs, _p(gate), gate.stride(0) if gate is not None else 0, x.shape[0], H, N, K,
+                                      _actf(w.dtype), _stream()), "seq_head_linear")
+    return y
+
+
+def seq_moe_route(logits, n_groups, keep, top, scale):
+    n, n_exp = logits.shape
+    ids = torch.empty((n, top), device=logits.device, dtype=torch.int32)
+    wts = torch.empty((n, top), device=logits.device, dtype=torch.float32)
+    check(lib().llark_seq_moe_route(_p(_req(logits, torch.float32)), logits.stride(0), _p(ids), _p(wts), n, n_exp,
+                                    int(n_groups), int(keep), int(top), float(scale), _stream()), "seq_moe_route")
+    return ids, wts
+
+
+def seq_moe_experts(x, ids, w_gate_up, w_down):
+    """x act [n_tok, C]; ids int32 [n_tok, top]; w_gate_up act [n_exp, 2*ff, C] (gate rows, then up rows);
+    w_down act [n_exp, C, ff] -> (z fp32 [n_tok*top, C] expert outputs in sorted order, pos_of int32 [n_tok*top])."""
+    L = lib()
+    n_tok, top = ids.shape
+    n_exp, ff2, C = w_gate_up.shape
+    ff = ff2 // 2
+    n_ent = n_tok * top
+    max_tiles = (n_ent + L.llark_seq_moe_tile_rows() - 1) // L.llark_seq_moe_tile_rows() + n_exp
+    ints = torch.empty(2 * n_ent + 3 * max_tiles + 1, device=x.device, dtype=torch.int32)
+    perm, pos_of = ints[:n_ent], ints[n_ent:2 * n_ent]
+    tiles, meta = ints[2 * n_ent:2 * n_ent + 3 * max_tiles], ints[2 * n_ent + 3 * max_tiles:]
+    check(L.llark_seq_moe_sort(_p(ids), n_ent, n_exp, _p(perm), _p(pos_of), _p(tiles), _p(meta), _stream()),
+          "seq_moe_sort")
+    act = torch.empty((n_ent, ff), device=x.device, dtype=x.dtype)
+    check(L.llark_seq_moe_up(_p(x), x.stride(0), _p(perm), top, _p(w_gate_up), _p(act), _p(tiles), _p(meta), max_tiles, ff,
+                             C, _actf(x.dtype), _stream()), "seq_moe_up")
+    z = torch.empty((n_ent, C), device=x.device, dtype=torch.float32)
+    check(L.llark_seq_moe_down(_p(act), _p(w_down), _p(z), _p(tiles), _p(meta), max_tiles, C, ff, _actf(x.dtype),
+                               _stream()), "seq_moe_down")
+    return z, pos_of
+
+
+def seq_tanh(u, act):
+    """tanh of an fp32 tensor -> `act`."""
+    _req(u, torch.float32)
+    y = torch.empty(u.shape, device=u.device, dtype=act)
+    check(lib().llark_seq_tanh(_p(u), _p(y), u.numel(), _actf(act), _stream()), "seq_tanh")
+    return y
