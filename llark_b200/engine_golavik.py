@@ -66,7 +66,7 @@ class GolavikEngine(LayerListEngine):
             runs.append({"pk": pk, "pass_vec": self.loop_step[t] if first else None,
                          "tail1": cache.add_store(carry, F32, zero_on_alloc=True),
                          "tail2": cache.add_store(carry, F32, zero_on_alloc=True) if layer.mlp is not None else None,
-                         "mixer": MIXERS[layer.type](pk["mixer"], cache, cfg.eps, self.act, None),
+                         "mixer": MIXERS[layer.type](pk["mixer"], cache, cfg.eps, self.act, self.max_positions),
                          "ff": FEED_FORWARDS[layer.mlp["kind"]](pk["ff"], self.act) if layer.mlp is not None else None})
         cache.layers = runs
         return cache

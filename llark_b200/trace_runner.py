@@ -26,7 +26,7 @@ def main(argv=None):
                     help="bfloat16: the serving kernels; float32: everything in true 32-bit")
     ap.add_argument("--out", required=True, help="folder the <step>.f32 files are written to")
     ap.add_argument("--max-tokens", type=int, default=None,
-                    help="most tokens live requests hold at any time (the slot stores do not depend on it)")
+                    help="most tokens live requests hold at any time (bounds a request's length where the model names no bound)")
     ap.add_argument("--device", default="cuda:0")
     a = ap.parse_args(argv)
 
@@ -36,6 +36,8 @@ def main(argv=None):
     torch.cuda.set_device(torch.device(a.device))
     model = load_model(a.model, dtype=dtype, device=a.device)
     engine = model.engine
+    if a.max_tokens and engine.max_positions is None:
+        engine.max_positions = int(a.max_tokens)  # no request outgrows what all live requests may hold: bounds the rings
     cache = model.new_cache()
     os.makedirs(a.out, exist_ok=True)
     slots = {}

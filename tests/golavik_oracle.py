@@ -230,3 +230,71 @@ def forward(cfg, W, tokens, return_residuals=False):
         res.append(x)
     logits = group_rms_norm(x, W["final.norm"], groups, eps) @ W["embed"].T
     return (logits, res) if return_residuals else logits
+
+
+# ------------------------------------------------------------------------------------------------ random checkpoints
+def random_weights(cfg, seed=0, ranks=(5, 7, 6), dtype=torch.float64):
+    """Random weights of a configuration, rounded to bfloat16 (what a checkpoint stores) and returned in `dtype`.
+    ranks: bottleneck sizes of the decay and gate projections of channel_delta and of the decay of general_delta."""
+    g = torch.Generator().manual_seed(seed)
+    C, V = cfg["width"], cfg["vocab"]
+    W = {}
+
+    def mat(name, out, inp, scale=1.0):
+        W[name] = torch.randn(out, inp, generator=g) * scale / math.sqrt(inp)
+
+    def vec(name, n, mean=0.0, std=1.0):
+        W[name] = mean + std * torch.randn(n, generator=g)
+
+    W["embed"] = torch.randn(V, C, generator=g)
+    vec("final.norm", C, 1.0, 0.1)
+    if cfg.get("loop"):
+        W["loop.step"] = torch.randn(cfg["loop"]["times"], C, generator=g) * 0.5
+    taps = cfg["canon"]["taps"]
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        vec(p + "norm1", C, 1.0, 0.1)
+        W[p + "canon1"] = torch.randn(C, taps, generator=g) * 0.3
+        x = p + "mix."
+        if L["type"] == "latent_attention":
+            H, D, P, E, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            mat(x + "q", H * (D + P), C, 2.0)
+            mat(x + "dkv", R + P, C, 2.0)
+            vec(x + "dkv.norm", R, 1.0, 0.1)
+            mat(x + "uk", H * D, R, 2.0)
+            mat(x + "uv", H * E, R)
+            mat(x + "g", H * E, C)
+            mat(x + "o", C, H * E)
+        elif L["type"] == "channel_delta":
+            H, G, D, E = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            for n, rows in (("q", G * D), ("k", G * D), ("v", H * E)):
+                mat(x + n, rows, C, 2.0)
+                W[x + n + ".conv"] = torch.randn(rows, m["conv"], generator=g) * 0.5
+            mat(x + "b", H, C)
+            W[x + "A_log"] = torch.rand(H, generator=g) * 2.0 - 2.0
+            vec(x + "norm", E, 1.0, 0.1)
+            mat(x + "a1", ranks[0], C)
+            mat(x + "a2", H * D, ranks[0], 2.0)
+            vec(x + "dt_bias", H * D, -1.0, 1.0)
+            mat(x + "g1", ranks[1], C)
+            mat(x + "g2", H * E, ranks[1], 2.0)
+            mat(x + "o", C, H * E)
+        else:
+            H, D = m["heads"], m["dim"]
+            for n in ("r", "k", "v", "a", "g"):
+                mat(x + n, H * D, C, 1.5)
+            vec(x + "a.b", H * D, 0.0, 0.5)
+            mat(x + "w1", ranks[2], C)
+            mat(x + "w2", H * D, ranks[2], 2.0)
+            vec(x + "w0", H * D, -0.5, 1.0)
+            vec(x + "norm", H * D, 1.0, 0.1)
+            mat(x + "o", C, H * D)
+        if L.get("mlp"):
+            W[p + "canon2"] = torch.randn(C, taps, generator=g) * 0.3
+            f, n = L["mlp"]["expert"]["ff"], L["mlp"]["router"]["experts"]
+            mat(p + "mlp.router", n, C, 2.0)
+            for e in range(n):
+                mat(f"{p}mlp.e{e}.gate", f, C)
+                mat(f"{p}mlp.e{e}.up", f, C)
+                mat(f"{p}mlp.e{e}.down", C, f)
+    return {k: v.to(torch.bfloat16).to(dtype) for k, v in W.items()}
