@@ -380,16 +380,24 @@ int llark_seq_head_linear(const void* x, int x_fp32, long long ldx, int x_hs, co
                           cudaStream_t stream);
 /* y = tanh(u), fp32 in, ACT out */
 int llark_seq_tanh(const float* u, void* y, long long n, int act_fp32, cudaStream_t stream);
+/* C[off[e] .. off[e+1]) = A[same rows] @ B[e]^T, e < n_seg; B bf16 [n_seg, N, K]; seg_off_host on the host */
+int llark_gemm_segments(const void* A, long long lda, const void* B, void* C, long long ldc, int c_fp32,
+                        const int* seg_off_host, int n_seg, int N, int K, cudaStream_t stream);
 /* routed mixture of experts (see csrc/seq_moe.cu) */
 int llark_seq_moe_route(const float* logits, long long ld, int* ids, float* wts, int n_tok, int n_exp, int n_groups,
                         int keep, int top, float scale, cudaStream_t stream);
 int llark_seq_moe_tile_rows(void);
-int llark_seq_moe_sort(const int* ids, int n_ent, int n_exp, int* perm, int* pos_of, int* tiles, int* meta,
+int llark_seq_moe_sort(const int* ids, int n_ent, int n_exp, int* perm, int* pos_of, int* tiles, int* meta, int* seg_off,
                        cudaStream_t stream);
+/* xs[p] = x[perm[p] / top] (rows in sorted order); act = silu(gu[:, :ff]) * gu[:, ff:] */
+int llark_seq_moe_gather(const void* x, long long ldx, const int* perm, int top, void* xs, int n_ent, int C, int act_fp32,
+                         cudaStream_t stream);
+int llark_seq_silu_mul(const void* gu, void* act, long long rows, int ff, int act_fp32, cudaStream_t stream);
 int llark_seq_moe_up(const void* x, long long ldx, const int* perm, int top, const void* w_gate_up, void* act,
-                     const int* tiles, const int* meta, int max_tiles, int ff, int K, int act_fp32, cudaStream_t stream);
+                     const int* tiles, const int* meta, int max_tiles, int n_ent, int ff, int K, int act_fp32,
+                     cudaStream_t stream);
 int llark_seq_moe_down(const void* act, const void* w_down, float* z, const int* tiles, const int* meta, int max_tiles,
-                       int C, int ff, int act_fp32, cudaStream_t stream);
+                       int n_ent, int C, int ff, int act_fp32, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -24,10 +24,11 @@ SEQ_SYMBOLS = [
     "llark_linear_simt_w32", "llark_seq_group_rmsnorm", "llark_seq_residual_combine", "llark_seq_conv_act",
     "llark_seq_delta_prep", "llark_seq_delta_scan", "llark_seq_head_norm_gate", "llark_seq_latent_prep",
     "llark_seq_head_linear", "llark_seq_moe_route", "llark_seq_moe_tile_rows", "llark_seq_moe_sort", "llark_seq_moe_up",
-    "llark_seq_moe_down", "llark_seq_tanh",
+    "llark_seq_moe_down", "llark_seq_tanh", "llark_seq_moe_gather", "llark_seq_silu_mul",
 ]
 # what libllark_serve.so (`make serve`: GEMM core + decode linears + the ops above) exports
-SERVE_SYMBOLS = SEQ_SYMBOLS + ["llark_last_cuda_error", "llark_init", "llark_gemm", "llark_gemm_ex", "llark_gemv"]
+SERVE_SYMBOLS = SEQ_SYMBOLS + ["llark_last_cuda_error", "llark_init", "llark_gemm", "llark_gemm_ex", "llark_gemv",
+                               "llark_gemm_segments"]
 # every symbol include/llark_b200.h declares (tests check that the library exports all of them)
 SYMBOLS = [
     "llark_last_cuda_error", "llark_gemm", "llark_gemm_ex", "llark_gemm_clear_cache", "llark_gemm_set_mode", "llark_gemm_get_mode", "llark_splice_scan", "llark_embed_splice_fwd",
@@ -40,7 +41,7 @@ SYMBOLS = [
     "llark_jb_conv_k3", "llark_jb_vq_encode", "llark_layernorm_fwd", "llark_jb_embed_tokens", "llark_jb_sparse_attn",
     "llark_jb_sparse_attn_tc",
     "llark_quick_gelu", "llark_add3", "llark_jb_pool", "llark_jb_pool_batched", "llark_colsum",
-    "llark_init", "llark_attn_bwd_rope", "llark_jb_label_cond", "llark_v32_split_tf32", "llark_v32_embed_splice_fwd", "llark_v32_rmsnorm_fwd", "llark_v32_rope",
+    "llark_gemm_segments", "llark_init", "llark_attn_bwd_rope", "llark_jb_label_cond", "llark_v32_split_tf32", "llark_v32_embed_splice_fwd", "llark_v32_rmsnorm_fwd", "llark_v32_rope",
     "llark_v32_swiglu_fwd", "llark_v32_attn_fwd", "llark_v32_ce_fwd",
 ] + SEQ_SYMBOLS
 
@@ -165,9 +166,12 @@ def lib():
             "llark_seq_head_linear": ([P, I, LL, I, P, P, LL, I, P, LL, I, I, I, I, I, P], I),
             "llark_seq_moe_route": ([P, LL, P, P, I, I, I, I, I, F, P], I),
             "llark_seq_moe_tile_rows": ([], I),
-            "llark_seq_moe_sort": ([P, I, I, P, P, P, P, P], I),
-            "llark_seq_moe_up": ([P, LL, P, I, P, P, P, P, I, I, I, I, P], I),
-            "llark_seq_moe_down": ([P, P, P, P, P, I, I, I, I, P], I),
+            "llark_seq_moe_sort": ([P, I, I, P, P, P, P, P, P], I),
+            "llark_seq_moe_gather": ([P, LL, P, I, P, I, I, I, P], I),
+            "llark_seq_silu_mul": ([P, P, LL, I, I, P], I),
+            "llark_seq_moe_up": ([P, LL, P, I, P, P, P, P, I, I, I, I, I, P], I),
+            "llark_seq_moe_down": ([P, P, P, P, P, I, I, I, I, I, P], I),
+            "llark_gemm_segments": ([P, LL, P, P, LL, I, P, I, I, I, P], I),
             "llark_seq_tanh": ([P, P, LL, I, P], I),
         }
         for name, (argtypes, restype) in sig.items():

@@ -118,7 +118,7 @@ class OpTimer:
     def __init__(self, names):
         from llark_b200 import ops
 
-        self.ops, self.names, self.saved, self.records = ops, names, {}, []
+        self.ops, self.names, self.saved, self.records, self.depth = ops, names, {}, [], 0
 
     def __enter__(self):
         for n in self.names:
@@ -126,9 +126,15 @@ class OpTimer:
             self.saved[n] = f
 
             def wrap(*a, __f=f, __n=n, **k):
+                if self.depth:  # an op that another timed op calls is part of that one
+                    return __f(*a, **k)
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
-                out = __f(*a, **k)
+                self.depth += 1
+                try:
+                    out = __f(*a, **k)
+                finally:
+                    self.depth -= 1
                 e1.record()
                 self.records.append((__n, e0, e1, a, k, out))
                 return out
@@ -173,6 +179,19 @@ def _op_work(name, a, k, out, ctx):
     if name == "seq_glr_scan":
         src, state, st, H, D, E = a[0], a[5], a[6], a[7], a[8], a[9]
         return _nbytes(src) + 2 * st.n_seq * H * D * E * 4 + st.n_tok * H * E * 4, 5.0 * st.n_tok * H * D * E
+    if name == "seq_delta_scan":
+        vec, v, state, st, H, D, E = a[0], a[1], a[2], a[3], a[4], a[5], a[6]
+        return (_nbytes(vec) + st.n_tok * H * E * 8 + 2 * st.n_seq * H * D * E * 4), 9.0 * st.n_tok * H * D * E
+    if name == "seq_moe_experts":
+        x, ids, wgu, wd = a[0], a[1], a[2], a[3]
+        n_ent, (n_exp, ff2, C) = ids.numel(), wgu.shape
+        hit = min(n_exp, n_ent)
+        return (hit * (ff2 * C + C * ff2 // 2) * wgu.element_size() + n_ent * C * (x.element_size() + 4)
+                + n_ent * ff2 * x.element_size()), 2.0 * n_ent * 3 * (ff2 // 2) * C
+    if name == "seq_head_linear":
+        x, w, y, N, K = a[0], a[2], a[3], k["N"], k["K"]
+        M, H = x.shape[0], w.shape[0]
+        return M * H * (K * x.element_size() + N * y.element_size()) + _nbytes(w), 2.0 * M * H * N * K
     if name == "seq_short_conv":
         return _nbytes(a[0]) + _nbytes(out), 0.0
     if name == "seq_qk_headnorm":
@@ -219,6 +238,158 @@ def op_table(records, ctx, peaks):
 KELUTAR_OPS = ["linear", "seq_embed", "seq_short_conv", "seq_add_rmsnorm", "seq_rmsnorm_rows", "seq_relu2",
                "seq_qk_headnorm", "seq_swa_attn", "seq_kv_ring_write", "seq_glr_scan", "seq_head_rmsnorm"]
 LLAMA_OPS = ["gemm", "gemv", "rmsnorm_fwd", "rope_", "attn_fwd", "attn_decode", "swiglu_fwd", "embed_splice_fwd"]
+
+
+GOLAVIK_OPS = ["linear", "linear_w32", "seq_embed", "seq_short_conv", "seq_group_rmsnorm", "seq_residual_combine",
+               "seq_conv_act", "seq_delta_prep", "seq_delta_scan", "seq_head_norm_gate", "seq_latent_prep",
+               "seq_head_linear", "seq_swa_attn", "seq_kv_ring_write", "seq_moe_route", "seq_moe_experts", "seq_tanh"]
+
+# (name, width, layers, heads, head dim, window, experts, top, expert ff, latent rank, rotated size, vocab): layers repeat
+# latent_attention, channel_delta, general_delta, channel_delta, each with a routed feed-forward; the Kelutar model beside it
+# has the same width, layer count, heads and window, and a dense feed-forward of top x expert-ff rows on its attention layers
+GOLAVIK_SIZES = [
+    ("g2048", 2048, 4, 16, 128, 1024, 32, 4, 1024, 192, 64, 32000),
+    ("g4096", 4096, 4, 32, 128, 2048, 64, 6, 1024, 192, 64, 32000),
+]
+
+
+def golavik_config(width, layers, heads, dim, window, experts, top, ff, rank, rot, vocab):
+    moe = {"kind": "moe", "expert": {"ff": ff},
+           "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": 8, "keep": 4}}}
+    kinds = [
+        {"type": "latent_attention", "mixer": {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": dim, "kv_rank": rank,
+                                               "scale": 1.0 / math.sqrt(dim + rot), "mask": {"size": window},
+                                               "rot": {"base": 10000.0, "dims": rot,
+                                                       "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0,
+                                                                   "slow": 1.0}}}},
+        {"type": "channel_delta", "mixer": {"heads": heads, "kv_heads": heads, "dim": dim, "vdim": dim, "conv": 4}},
+        {"type": "general_delta", "mixer": {"heads": heads, "dim": dim}},
+        {"type": "channel_delta", "mixer": {"heads": heads, "kv_heads": heads, "dim": dim, "vdim": dim, "conv": 4}}]
+    return {"architecture": "Golavik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5, "groups": 2},
+            "canon": {"taps": 4}, "loop": None,
+            "layers": [dict(kinds[i % 4], mlp=moe) for i in range(layers)]}
+
+
+def golavik_random_weights(cfg, device, seed=0, low_rank=64):
+    g = torch.Generator(device=device).manual_seed(seed)
+    C = cfg["width"]
+
+    def mat(o, i, s=None):
+        return (torch.randn(o, i, device=device, generator=g) * (s or 1.0 / math.sqrt(i))).to(BF16)
+
+    def vec(n, mean=1.0, s=0.1):
+        return (mean + torch.randn(n, device=device, generator=g) * s).to(BF16)
+
+    W = {"embed": mat(cfg["vocab"], C, 1.0 / math.sqrt(C)), "final.norm": vec(C)}
+    taps = cfg["canon"]["taps"]
+    for i, layer in enumerate(cfg["layers"]):
+        p, m = "l%d." % i, layer["mixer"]
+        x = p + "mix."
+        W[p + "norm1"], W[p + "canon1"], W[p + "canon2"] = vec(C), mat(C, taps, 0.3), mat(C, taps, 0.3)
+        H, D = m["heads"], m["dim"]
+        if layer["type"] == "latent_attention":
+            P, E, R = m["rot_dim"], m["vdim"], m["kv_rank"]
+            W.update({x + "q": mat(H * (D + P), C), x + "dkv": mat(R + P, C), x + "dkv.norm": vec(R),
+                      x + "uk": mat(H * D, R), x + "uv": mat(H * E, R), x + "g": mat(H * E, C), x + "o": mat(C, H * E)})
+        elif layer["type"] == "channel_delta":
+            G, E = m["kv_heads"], m["vdim"]
+            for n, rows in (("q", G * D), ("k", G * D), ("v", H * E)):
+                W[x + n], W[x + n + ".conv"] = mat(rows, C), mat(rows, m["conv"], 0.5)
+            W.update({x + "b": mat(H, C), x + "A_log": vec(H, -1.0, 0.5), x + "norm": vec(E), x + "a1": mat(low_rank, C),
+                      x + "a2": mat(H * D, low_rank), x + "dt_bias": vec(H * D, -1.0, 1.0), x + "g1": mat(low_rank, C),
+                      x + "g2": mat(H * E, low_rank), x + "o": mat(C, H * E)})
+        else:
+            for n in ("r", "k", "v", "a", "g"):
+                W[x + n] = mat(H * D, C)
+            W.update({x + "a.b": vec(H * D, 0.0, 0.5), x + "w1": mat(low_rank, C), x + "w2": mat(H * D, low_rank),
+                      x + "w0": vec(H * D, -0.5, 1.0), x + "norm": vec(H * D), x + "o": mat(C, H * D)})
+        r, f = layer["mlp"]["router"], layer["mlp"]["expert"]["ff"]
+        W[p + "mlp.router"] = mat(r["experts"], C)
+        for e in range(r["experts"]):
+            W.update({"%smlp.e%d.gate" % (p, e): mat(f, C), "%smlp.e%d.up" % (p, e): mat(f, C),
+                      "%smlp.e%d.down" % (p, e): mat(C, f)})
+    return W
+
+
+def bench_native(tag, eng, op_names, out, vocab, peaks, steps, warmup, flush, g, prefill_batch, prompt, decode_batches,
+                 context):
+    """Prefill and decode timings and op tables of one native decoder (an engine with step / new_cache) into out."""
+    state = {}
+
+    def setup_prefill():
+        state["cache"] = eng.new_cache(n_slots=prefill_batch)
+        state["slots"] = [state["cache"].alloc() for _ in range(prefill_batch)]
+
+    toks = torch.randint(0, vocab, (prefill_batch, prompt), generator=torch.Generator().manual_seed(0)).tolist()
+    ms = timed(lambda: eng.step(state["cache"], state["slots"], toks), warmup, steps, flush, setup=setup_prefill)
+    out["prefill"][tag + "_tokens_per_s"] = round(prefill_batch * prompt / ms * 1e3, 1)
+    out["prefill"][tag + "_ms"] = round(ms, 3)
+    for _ in range(2):  # the second pass is the one that is read: no first-use cost of the wrappers
+        setup_prefill()
+        with OpTimer(op_names) as t:
+            eng.step(state["cache"], state["slots"], toks)
+    out["prefill"][tag + "_ops"] = op_table(t.records, {}, peaks)
+    state.clear()
+    for B in decode_batches:
+        cache = eng.new_cache(n_slots=B)
+        slots = [cache.alloc() for _ in range(B)]
+        eng.step(cache, slots, torch.randint(0, vocab, (B, context), generator=g).tolist())
+        nxt = torch.randint(0, vocab, (B, 1), generator=g).tolist()
+        ms = timed(lambda: eng.step(cache, slots, nxt), warmup, max(steps, 10), flush)
+        out["decode"]["%s_b%d_tokens_per_s" % (tag, B)] = round(B / ms * 1e3, 1)
+        out["decode"]["%s_b%d_ms" % (tag, B)] = round(ms, 3)
+        if B == decode_batches[-1] or B == 8:
+            for _ in range(2):
+                with OpTimer(op_names) as t:
+                    eng.step(cache, slots, nxt)
+            out["decode"]["%s_b%d_ops" % (tag, B)] = op_table(t.records, {"context": context}, peaks)
+        del cache
+    torch.cuda.empty_cache()
+
+
+def bench_size_golavik(name, width, layers, heads, dim, window, experts, top, ff, rank, rot, vocab, peaks, steps, warmup,
+                       prefill_batch=4, prompt=2048, decode_batches=(1, 8, 32), context=1024):
+    """Golavik beside Kelutar (the closest existing decoder: a layer list of recurrences and window attention on the same
+    step function, cache and linears) at equal width, layer count, heads and window."""
+    from llark_b200.models.golavik import GolavikConfig, GolavikForCausalLM
+    from llark_b200.models.kelutar import KelutarConfig, KelutarForCausalLM
+
+    flush = _Flush()
+    out = {"size": name, "width": width, "layers": layers, "heads": heads, "head_dim": dim, "window": window,
+           "experts": experts, "top": top, "expert_ff": ff, "kv_rank": rank, "rot_dim": rot, "vocab": vocab,
+           "prefill": {"batch": prefill_batch, "prompt": prompt}, "decode": {"context": context}}
+    g = torch.Generator().manual_seed(0)
+    cfg = golavik_config(width, layers, heads, dim, window, experts, top, ff, rank, rot, vocab)
+    gm = GolavikForCausalLM(GolavikConfig.from_dict(cfg), golavik_random_weights(cfg, "cuda"), dtype=BF16)
+    bench_native("golavik", gm.engine, GOLAVIK_OPS, out, vocab, peaks, steps, warmup, flush, g, prefill_batch, prompt,
+                 decode_batches, context)
+    del gm
+    torch.cuda.empty_cache()
+    kcfg = kelutar_config(width, layers, heads, dim, window, top * ff, vocab, max(prompt, context) + 64)
+    km = KelutarForCausalLM(KelutarConfig.from_dict(kcfg), kelutar_random_weights(kcfg, "cuda"), dtype=BF16)
+    bench_native("kelutar", km.engine, KELUTAR_OPS, out, vocab, peaks, steps, warmup, flush, g, prefill_batch, prompt,
+                 decode_batches, context)
+    del km
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_golavik(args, peaks, peaks_kind, emit):
+    from llark_b200 import ops
+
+    ops.init()
+    t0 = time.time()
+    sizes = [s for s in GOLAVIK_SIZES if not os.environ.get("LLARK_BENCH_SIZE") or s[0] == os.environ["LLARK_BENCH_SIZE"]]
+    results = [bench_size_golavik(*s, peaks=peaks, steps=args.steps, warmup=max(args.warmup, 3)) for s in sizes]
+    head = results[0]
+    emit({"metric": "generation tokens/s, Golavik beside Kelutar at equal size (prefill of %d x %d tokens)"
+                    % (head["prefill"]["batch"], head["prefill"]["prompt"]),
+          "value": head["prefill"]["golavik_tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+          "warmup": max(args.warmup, 3), "ms_per_step": head["prefill"]["golavik_ms"], "higher_is_better": True,
+          "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, random weights",
+          "config": {"model": "Golavik " + head["size"], "l2": "256 MB fill between timed steps",
+                     "peaks": peaks_kind, "hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"]},
+          "sizes": results, "wall_s": round(time.time() - t0, 1)})
 
 
 def bench_size(name, width, layers, heads, dim, window, ff, vocab, peaks, steps, warmup, prefill_batch=4,

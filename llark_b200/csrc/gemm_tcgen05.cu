@@ -1354,3 +1354,23 @@ extern "C" void llark_gemm_clear_cache(void) {
     std::lock_guard<std::mutex> lk(g_mu);
     g_map_cache.clear();
 }
+
+// Runs of rows that each multiply their own weight block: C[off[e] .. off[e+1]) = A[same rows] @ B[e]^T for e < n_seg, with
+// B [n_seg, N, K] stacked and the run boundaries on the host (a routed feed-forward after its rows have been sorted by
+// expert). One call instead of n_seg trips through the language binding; bf16 operands, bf16 or fp32 output.
+extern "C" int llark_gemm_segments(const void* A, long long lda, const void* B, void* C, long long ldc, int c_fp32,
+                                   const int* seg_off_host, int n_seg, int N, int K, cudaStream_t stream) {
+    if (!A || !B || !C || !seg_off_host || n_seg <= 0 || N <= 0 || K <= 0) return LLARK_EINVAL;
+    const char* a = static_cast<const char*>(A);
+    const char* b = static_cast<const char*>(B);
+    char* c = static_cast<char*>(C);
+    for (int e = 0; e < n_seg; ++e) {
+        const int r0 = seg_off_host[e], rows = seg_off_host[e + 1] - r0;
+        if (rows <= 0) continue;
+        const int rc = llark_gemm(a + (long long)r0 * lda * 2, 0, lda, b + (long long)e * N * K * 2, 0, K,
+                                  c + (long long)r0 * ldc * (c_fp32 ? 4 : 2), ldc, c_fp32, nullptr, 0, nullptr, 0, rows, N, K,
+                                  0, 0, stream);
+        if (rc != LLARK_OK) return rc;
+    }
+    return LLARK_OK;
+}

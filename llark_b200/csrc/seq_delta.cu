@@ -135,8 +135,9 @@ __global__ void delta_prep_kernel(int rule, const float* __restrict__ q, long lo
 }
 
 // ------------------------------------------------------------------------------------------------ the recurrence
-// Block per (column slice, head, request). R adjacent lanes share column e of S; lane r owns rows r * DPT .. + DPT - 1 in
-// registers and the partial sums over rows are added by shuffle. The vectors and values of TS tokens are brought to
+// Block per (column slice, head, request). R adjacent lanes share column e of S; lane r owns the 4-row groups r, r + R,
+// r + 2R, ... (rows 4 (r + R i) + c) in registers, so that the R lanes read adjacent 16-byte pieces of a vector (no bank
+// conflicts; lanes of other columns get the same words by broadcast), and the partial sums over rows are added by shuffle. The vectors and values of TS tokens are brought to
 // shared memory with cp.async while the previous TS are computed. Rows d >= D are zero padding (DPT * R >= D).
 __device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
@@ -150,7 +151,7 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
 }
 
 template <int DPT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 1)
 delta_scan_kernel(const float* __restrict__ vec, const float* __restrict__ v, long long v_ld, float* __restrict__ state,
                   float* __restrict__ o, const int* __restrict__ cu, const int* __restrict__ slot, int H, int D, int E,
                   int R, int cols, int ts) {
@@ -167,7 +168,7 @@ delta_scan_kernel(const float* __restrict__ vec, const float* __restrict__ v, lo
     float* sp = state + (((long long)slot[b] * H + h) * D) * E;
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
-        const int d = r * DPT + i;
+        const int d = 4 * (r + R * (i >> 2)) + (i & 3);
         S[i] = (live && d < D) ? sp[(long long)d * E + e] : 0.f;
     }
     for (int i = threadIdx.x; i < 2 * stage_floats; i += blockDim.x) sm[i] = 0.f;  // padding rows stay zero
@@ -176,7 +177,14 @@ delta_scan_kernel(const float* __restrict__ vec, const float* __restrict__ v, lo
     auto issue = [&](int tok0, int st) {
         float* base = sm + st * stage_floats;
         const int cnt = n - tok0 < ts ? n - tok0 : ts;
-        if (vec16) {
+        if (vec16 && Dp == D) {  // a token's five vectors are one contiguous run on both sides
+            const int per = 5 * D / 4;
+            for (int tk = 0; tk < cnt; ++tk) {
+                const float* src = vec + ((long long)(row0 + tok0 + tk) * H + h) * 5 * D;
+                float* dst = base + tk * 5 * Dp;
+                for (int i = threadIdx.x; i < per; i += blockDim.x) cp_async16(dst + 4 * i, src + 4 * i);
+            }
+        } else if (vec16) {
             const int per = 5 * D / 4, dq = D / 4;
             for (int i = threadIdx.x; i < cnt * per; i += blockDim.x) {
                 const int tk = i / per, rem = i % per, which = rem / dq, d4 = rem % dq;
@@ -192,8 +200,8 @@ delta_scan_kernel(const float* __restrict__ vec, const float* __restrict__ v, lo
             }
         }
         float* sv = base + ts * 5 * Dp;
-        for (int i = threadIdx.x; i < cnt * cols; i += blockDim.x) {
-            const int tk = i / cols, c = i % cols;
+        for (int i = threadIdx.x; i < cnt * cols; i += blockDim.x) {  // cols is a power of two
+            const int tk = i / cols, c = i & (cols - 1);
             if (e0 + c < E) cp_async4(sv + tk * cols + c, v + (long long)(row0 + tok0 + tk) * v_ld + (long long)h * E + e0 + c);
         }
         cp_async_commit();
@@ -212,35 +220,37 @@ delta_scan_kernel(const float* __restrict__ vec, const float* __restrict__ v, lo
         const float* sv = base + ts * 5 * Dp;
         const int cnt = n - tok0 < ts ? n - tok0 : ts;
         for (int tk = 0; tk < cnt; ++tk) {
-            const float4* pq = reinterpret_cast<const float4*>(base + (tk * 5 + 0) * Dp + r * DPT);
-            const float4* pz = reinterpret_cast<const float4*>(base + (tk * 5 + 1) * Dp + r * DPT);
-            const float4* pd = reinterpret_cast<const float4*>(base + (tk * 5 + 2) * Dp + r * DPT);
-            const float4* p1 = reinterpret_cast<const float4*>(base + (tk * 5 + 3) * Dp + r * DPT);
-            const float4* p2 = reinterpret_cast<const float4*>(base + (tk * 5 + 4) * Dp + r * DPT);
-            float zs = 0.f;
+            const float4* pq = reinterpret_cast<const float4*>(base + (tk * 5 + 0) * Dp) + r;
+            const float4* pz = reinterpret_cast<const float4*>(base + (tk * 5 + 1) * Dp) + r;
+            const float4* pd = reinterpret_cast<const float4*>(base + (tk * 5 + 2) * Dp) + r;
+            const float4* p1 = reinterpret_cast<const float4*>(base + (tk * 5 + 3) * Dp) + r;
+            const float4* p2 = reinterpret_cast<const float4*>(base + (tk * 5 + 4) * Dp) + r;
+            float z0 = 0.f, z1 = 0.f, z2 = 0.f, z3 = 0.f;  // four chains instead of one
 #pragma unroll
             for (int i = 0; i < DPT / 4; ++i) {
-                const float4 z = pz[i];
-                zs = fmaf(z.x, S[4 * i], zs);
-                zs = fmaf(z.y, S[4 * i + 1], zs);
-                zs = fmaf(z.z, S[4 * i + 2], zs);
-                zs = fmaf(z.w, S[4 * i + 3], zs);
+                const float4 z = pz[R * i];
+                z0 = fmaf(z.x, S[4 * i], z0);
+                z1 = fmaf(z.y, S[4 * i + 1], z1);
+                z2 = fmaf(z.z, S[4 * i + 2], z2);
+                z3 = fmaf(z.w, S[4 * i + 3], z3);
             }
+            float zs = (z0 + z1) + (z2 + z3);
             for (int m = 1; m < R; m <<= 1) zs += __shfl_xor_sync(0xffffffffu, zs, m);
             const float vv = sv[tk * cols + col];
-            float os = 0.f;
+            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
             for (int i = 0; i < DPT / 4; ++i) {
-                const float4 dd = pd[i], a = p1[i], c = p2[i], qq = pq[i];
+                const float4 dd = pd[R * i], a = p1[R * i], c = p2[R * i], qq = pq[R * i];
                 S[4 * i] = fmaf(c.x, vv, fmaf(a.x, zs, dd.x * S[4 * i]));
                 S[4 * i + 1] = fmaf(c.y, vv, fmaf(a.y, zs, dd.y * S[4 * i + 1]));
                 S[4 * i + 2] = fmaf(c.z, vv, fmaf(a.z, zs, dd.z * S[4 * i + 2]));
                 S[4 * i + 3] = fmaf(c.w, vv, fmaf(a.w, zs, dd.w * S[4 * i + 3]));
-                os = fmaf(qq.x, S[4 * i], os);
-                os = fmaf(qq.y, S[4 * i + 1], os);
-                os = fmaf(qq.z, S[4 * i + 2], os);
-                os = fmaf(qq.w, S[4 * i + 3], os);
+                o0 = fmaf(qq.x, S[4 * i], o0);
+                o1 = fmaf(qq.y, S[4 * i + 1], o1);
+                o2 = fmaf(qq.z, S[4 * i + 2], o2);
+                o3 = fmaf(qq.w, S[4 * i + 3], o3);
             }
+            float os = (o0 + o1) + (o2 + o3);
             for (int m = 1; m < R; m <<= 1) os += __shfl_xor_sync(0xffffffffu, os, m);
             if (r == 0 && live) o[(long long)(row0 + tok0 + tk) * H * E + (long long)h * E + e] = os;
         }
@@ -248,7 +258,7 @@ delta_scan_kernel(const float* __restrict__ vec, const float* __restrict__ v, lo
     }
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
-        const int d = r * DPT + i;
+        const int d = 4 * (r + R * (i >> 2)) + (i & 3);
         if (live && d < D) sp[(long long)d * E + e] = S[i];
     }
 }

@@ -1,9 +1,10 @@
 // Routed mixture of experts on the generation path: every token uses `top` of n small gated feed-forwards
-// down(silu(gate x) * (up x)). No step of it returns to the host: the router picks experts on the device, one kernel sorts
-// the (token, choice) entries by expert and cuts each expert's run into row tiles, and two grouped GEMM launches walk
-// that tile list (rows gathered through the sort permutation). The weighted sum over a token's choices is taken in the
-// order of the choices when the residual is assembled (llark_seq_residual_combine), so a token's result does not depend
-// on what else is in the batch.
+// down(silu(gate x) * (up x)). The router picks experts on the device, one kernel sorts the (token, choice) entries by
+// expert and cuts each expert's run into row tiles, and two grouped GEMM launches walk that tile list (rows gathered
+// through the sort permutation) without a return to the host. Large bf16 steps instead read the segment sizes back once
+// and run every expert's rows through the tcgen05 GEMM core (llark_seq_moe_gather, the GEMMs, llark_seq_silu_mul). The
+// weighted sum over a token's choices is taken in the order of the choices when the residual is assembled
+// (llark_seq_residual_combine), so a token's result does not depend on what else is in the batch.
 //
 //   llark_seq_moe_route     scores = sigmoid(logits) fp32; experts form `n_groups` groups of neighbours, a group's score
 //                           is the sum of its two best, only experts of the best `keep` groups can be chosen; the `top`
@@ -35,6 +36,7 @@ template <> __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p,
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
 
 constexpr int kTileRows = 64;
+constexpr int kRowsRouteMaxEntries = 512;  // steps up to this many (token, choice) entries take the weight-streaming kernel
 
 // ------------------------------------------------------------------------------------------------ router
 // Warp per token; scores in shared memory. Ties go to the lower expert / group number.
@@ -118,7 +120,8 @@ __global__ void route_kernel(const float* __restrict__ logits, long long ld, int
 // ------------------------------------------------------------------------------------------------ sort by expert
 // One block. meta[0] = number of tiles; tiles[i] = (expert, first sorted row, rows).
 __global__ void sort_kernel(const int* __restrict__ ids, int n_ent, int n_exp, int* __restrict__ perm,
-                            int* __restrict__ pos_of, int* __restrict__ tiles, int* __restrict__ meta) {
+                            int* __restrict__ pos_of, int* __restrict__ tiles, int* __restrict__ meta,
+                            int* __restrict__ seg_off) {
     extern __shared__ int si[];
     int* cnt = si;               // [n_exp]
     int* off = cnt + n_exp;      // [n_exp + 1]
@@ -143,6 +146,8 @@ __global__ void sort_kernel(const int* __restrict__ ids, int n_ent, int n_exp, i
         meta[0] = nt;
     }
     __syncthreads();
+    if (seg_off)
+        for (int e = threadIdx.x; e <= n_exp; e += blockDim.x) seg_off[e] = off[e];
     for (int i = threadIdx.x; i < n_ent; i += blockDim.x) {
         const int e = ids[i];
         const int p = off[e] + atomicAdd(&cur[e], 1);
@@ -213,6 +218,107 @@ grouped_linear_kernel(const T* __restrict__ A, long long lda, const int* __restr
         }
 }
 
+// Few rows per expert (decode): a warp owns one output column of one row tile and streams its weight row (DUAL: the gate
+// and the up row) once in 16-byte pieces; the tile's rows come from L1 / L2, eight at a time.
+template <typename T, typename TC, bool DUAL>
+__global__ void __launch_bounds__(256)
+grouped_rows_kernel(const T* __restrict__ A, long long lda, const int* __restrict__ perm, int top,
+                    const T* __restrict__ W, TC* __restrict__ Cm, long long ldc, const int* __restrict__ tiles,
+                    const int* __restrict__ meta, int N, int K, int vec_ok) {
+    constexpr int MB = 8, VEC = 16 / (int)sizeof(T);
+    if ((int)blockIdx.y >= meta[0]) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (n >= N) return;
+    const int ex = tiles[3 * blockIdx.y], r0 = tiles[3 * blockIdx.y + 1], nr = tiles[3 * blockIdx.y + 2];
+    const T* w1 = W + ((long long)ex * (DUAL ? 2 : 1) * N + n) * K;
+    const T* w2 = w1 + (long long)N * K;
+    for (int m0 = 0; m0 < nr; m0 += MB) {
+        const T* ar[MB];
+#pragma unroll
+        for (int m = 0; m < MB; ++m) {
+            const int p = r0 + (m0 + m < nr ? m0 + m : nr - 1);
+            ar[m] = A + (long long)(perm ? perm[p] / top : p) * lda;
+        }
+        float acc[MB], acc2[MB];
+#pragma unroll
+        for (int m = 0; m < MB; ++m) acc[m] = acc2[m] = 0.f;
+        int k0 = 0;
+        if (vec_ok) {
+            const int kv = K / VEC;
+            for (int v = lane; v < kv; v += 32) {
+                const uint4 wa = __ldcs(reinterpret_cast<const uint4*>(w1) + v);
+                uint4 wb = wa;
+                if (DUAL) wb = __ldcs(reinterpret_cast<const uint4*>(w2) + v);
+                const T* pa = reinterpret_cast<const T*>(&wa);
+                const T* pb = reinterpret_cast<const T*>(&wb);
+#pragma unroll
+                for (int m = 0; m < MB; ++m) {
+                    if (m0 + m < nr) {
+                        const uint4 av = __ldg(reinterpret_cast<const uint4*>(ar[m]) + v);
+                        const T* px = reinterpret_cast<const T*>(&av);
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) {
+                            const float xv = ldf(px + e);
+                            acc[m] = fmaf(xv, ldf(pa + e), acc[m]);
+                            if (DUAL) acc2[m] = fmaf(xv, ldf(pb + e), acc2[m]);
+                        }
+                    }
+                }
+            }
+            k0 = kv * VEC;
+        }
+        for (int k = k0 + lane; k < K; k += 32) {
+            const float wa = ldf(w1 + k), wb = DUAL ? ldf(w2 + k) : 0.f;
+#pragma unroll
+            for (int m = 0; m < MB; ++m)
+                if (m0 + m < nr) {
+                    const float xv = ldf(ar[m] + k);
+                    acc[m] = fmaf(xv, wa, acc[m]);
+                    if (DUAL) acc2[m] = fmaf(xv, wb, acc2[m]);
+                }
+        }
+#pragma unroll
+        for (int m = 0; m < MB; ++m) {
+            float y = warp_sum(acc[m]);
+            if (DUAL) {
+                const float u = warp_sum(acc2[m]);
+                y = y * sigmoidf_(y) * u;
+            }
+            if (lane == 0 && m0 + m < nr) stf(Cm + (long long)(r0 + m0 + m) * ldc + n, y);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ dense-GEMM route
+// Large steps run each expert's rows through the framework's GEMM core instead: rows gathered into sorted order first,
+// silu(gate) * up afterwards.
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ x, long long ldx, const int* __restrict__ perm, int top,
+                                   T* __restrict__ xs, int C) {
+    const long long p = blockIdx.x;
+    const T* src = x + (long long)(perm[p] / top) * ldx;
+    T* dst = xs + p * C;
+    if ((C * (int)sizeof(T)) % 16 == 0 && (ldx * (long long)sizeof(T)) % 16 == 0) {
+        const int nv = C * (int)sizeof(T) / 16;
+        for (int i = threadIdx.x; i < nv; i += blockDim.x)
+            reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+    } else {
+        for (int i = threadIdx.x; i < C; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ act, long long rows, int ff) {
+    const long long n = rows * ff;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / ff;
+        const int c = (int)(i % ff);
+        const float g = ldf(gu + r * 2 * ff + c), u = ldf(gu + r * 2 * ff + ff + c);
+        stf(act + i, g * sigmoidf_(g) * u);
+    }
+}
+
 }  // namespace moe
 }  // namespace llark
 
@@ -236,19 +342,34 @@ extern "C" int llark_seq_moe_route(const float* logits, long long ld, int* ids, 
 extern "C" int llark_seq_moe_tile_rows(void) { return kTileRows; }
 
 extern "C" int llark_seq_moe_sort(const int* ids, int n_ent, int n_exp, int* perm, int* pos_of, int* tiles, int* meta,
-                                  cudaStream_t st) {
+                                  int* seg_off, cudaStream_t st) {
     if (n_ent <= 0 || n_exp <= 0 || !ids || !perm || !pos_of || !tiles || !meta) return LLARK_EINVAL;
     const size_t smem = sizeof(int) * (3 * (size_t)n_exp + 1);
     if (smem > 48 * 1024) return LLARK_EINVAL;
-    sort_kernel<<<1, 1024, smem, st>>>(ids, n_ent, n_exp, perm, pos_of, tiles, meta);
+    sort_kernel<<<1, 1024, smem, st>>>(ids, n_ent, n_exp, perm, pos_of, tiles, meta, seg_off);
     return check_launch();
 }
 
 extern "C" int llark_seq_moe_up(const void* x, long long ldx, const int* perm, int top, const void* w_gate_up, void* act,
-                                const int* tiles, const int* meta, int max_tiles, int ff, int K, int act_fp32,
+                                const int* tiles, const int* meta, int max_tiles, int n_ent, int ff, int K, int act_fp32,
                                 cudaStream_t st) {
     if (max_tiles <= 0 || ff <= 0 || K <= 0 || top <= 0 || !x || !perm || !w_gate_up || !act || !tiles || !meta)
         return LLARK_EINVAL;
+    if (n_ent <= kRowsRouteMaxEntries) {  // a handful of rows per expert: stream the weights once
+        dim3 g2((ff + 7) / 8, max_tiles);
+        const int esz = act_fp32 ? 4 : 2, vec = 16 / esz;
+        const int vec_ok = (K % vec == 0) && (ldx % vec == 0) &&
+                           (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w_gate_up)) & 15) == 0);
+        if (act_fp32)
+            grouped_rows_kernel<float, float, true><<<g2, 256, 0, st>>>((const float*)x, ldx, perm, top,
+                                                                        (const float*)w_gate_up, (float*)act, ff, tiles,
+                                                                        meta, ff, K, vec_ok);
+        else
+            grouped_rows_kernel<bf16_t, bf16_t, true><<<g2, 256, 0, st>>>((const bf16_t*)x, ldx, perm, top,
+                                                                          (const bf16_t*)w_gate_up, (bf16_t*)act, ff,
+                                                                          tiles, meta, ff, K, vec_ok);
+        return check_launch();
+    }
     dim3 grid((ff + 63) / 64, max_tiles);
     if (act_fp32)
         grouped_linear_kernel<float, float, true><<<grid, 256, 0, st>>>((const float*)x, ldx, perm, top,
@@ -262,8 +383,23 @@ extern "C" int llark_seq_moe_up(const void* x, long long ldx, const int* perm, i
 }
 
 extern "C" int llark_seq_moe_down(const void* act, const void* w_down, float* z, const int* tiles, const int* meta,
-                                  int max_tiles, int C, int ff, int act_fp32, cudaStream_t st) {
+                                  int max_tiles, int n_ent, int C, int ff, int act_fp32, cudaStream_t st) {
     if (max_tiles <= 0 || ff <= 0 || C <= 0 || !act || !w_down || !z || !tiles || !meta) return LLARK_EINVAL;
+    if (n_ent <= kRowsRouteMaxEntries) {
+        dim3 g2((C + 7) / 8, max_tiles);
+        const int esz = act_fp32 ? 4 : 2, vec = 16 / esz;
+        const int vec_ok = (ff % vec == 0) &&
+                           (((reinterpret_cast<uintptr_t>(act) | reinterpret_cast<uintptr_t>(w_down)) & 15) == 0);
+        if (act_fp32)
+            grouped_rows_kernel<float, float, false><<<g2, 256, 0, st>>>((const float*)act, ff, nullptr, 1,
+                                                                         (const float*)w_down, z, C, tiles, meta, C, ff,
+                                                                         vec_ok);
+        else
+            grouped_rows_kernel<bf16_t, float, false><<<g2, 256, 0, st>>>((const bf16_t*)act, ff, nullptr, 1,
+                                                                          (const bf16_t*)w_down, z, C, tiles, meta, C, ff,
+                                                                          vec_ok);
+        return check_launch();
+    }
     dim3 grid((C + 63) / 64, max_tiles);
     if (act_fp32)
         grouped_linear_kernel<float, float, false><<<grid, 256, 0, st>>>((const float*)act, ff, nullptr, 1,
@@ -271,5 +407,26 @@ extern "C" int llark_seq_moe_down(const void* act, const void* w_down, float* z,
     else
         grouped_linear_kernel<bf16_t, float, false><<<grid, 256, 0, st>>>((const bf16_t*)act, ff, nullptr, 1,
                                                                           (const bf16_t*)w_down, z, C, tiles, meta, C, ff);
+    return check_launch();
+}
+
+extern "C" int llark_seq_moe_gather(const void* x, long long ldx, const int* perm, int top, void* xs, int n_ent, int C,
+                                    int act_fp32, cudaStream_t st) {
+    if (n_ent <= 0 || C <= 0 || top <= 0 || !x || !perm || !xs) return LLARK_EINVAL;
+    if (act_fp32)
+        gather_rows_kernel<float><<<n_ent, 128, 0, st>>>((const float*)x, ldx, perm, top, (float*)xs, C);
+    else
+        gather_rows_kernel<bf16_t><<<n_ent, 128, 0, st>>>((const bf16_t*)x, ldx, perm, top, (bf16_t*)xs, C);
+    return check_launch();
+}
+
+extern "C" int llark_seq_silu_mul(const void* gu, void* act, long long rows, int ff, int act_fp32, cudaStream_t st) {
+    if (rows <= 0 || ff <= 0 || !gu || !act) return LLARK_EINVAL;
+    const long long n = rows * ff;
+    const unsigned grid = (unsigned)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    if (act_fp32)
+        silu_mul_kernel<float><<<grid, 256, 0, st>>>((const float*)gu, (float*)act, rows, ff);
+    else
+        silu_mul_kernel<bf16_t><<<grid, 256, 0, st>>>((const bf16_t*)gu, (bf16_t*)act, rows, ff);
     return check_launch();
 }

@@ -449,6 +449,26 @@ __global__ void residual_combine_kernel(const float* __restrict__ x, const float
     }
 }
 
+// Few rows, 32-bit weights (router logits while decoding): block per row, the row in shared memory as floats, a warp per
+// output column at a time.
+template <typename TA>
+__global__ void linear_rows_w32_kernel(const TA* __restrict__ A, long long lda, const float* __restrict__ W,
+                                       long long ldw, float* __restrict__ Cm, long long ldc,
+                                       const float* __restrict__ bias, int N, int K) {
+    extern __shared__ float xrow[];
+    const long long m = blockIdx.x;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) xrow[k] = ldf(A + m * lda + k);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int n = warp; n < N; n += nw) {
+        const float* wr = W + (long long)n * ldw;
+        float acc = 0.f;
+        for (int k = lane; k < K; k += 32) acc = fmaf(xrow[k], wr[k], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) Cm[m * ldc + n] = acc + (bias ? bias[n] : 0.f);
+    }
+}
+
 static int norm_threads(int C) {
     int t = 32;
     while (t < C / 4 && t < 512) t <<= 1;
@@ -614,6 +634,14 @@ extern "C" int llark_linear_simt_w32(const void* A, long long lda, const float* 
                                      long long ldc, const float* bias, int M, int N, int K, int in_fp32,
                                      cudaStream_t st) {
     if (M <= 0 || N <= 0 || K <= 0 || !A || !W || !C || lda < K || ldw < K || ldc < N) return LLARK_EINVAL;
+    if (M <= 128 && (size_t)K * sizeof(float) <= 48 * 1024) {
+        if (in_fp32)
+            linear_rows_w32_kernel<float><<<M, 256, K * sizeof(float), st>>>((const float*)A, lda, W, ldw, C, ldc, bias, N, K);
+        else
+            linear_rows_w32_kernel<bf16_t><<<M, 256, K * sizeof(float), st>>>((const bf16_t*)A, lda, W, ldw, C, ldc, bias, N,
+                                                                            K);
+        return check_launch();
+    }
     dim3 grid((N + 63) / 64, (M + 63) / 64);
     if (in_fp32)
         linear_simt_kernel<float, float, float><<<grid, 256, 0, st>>>((const float*)A, lda, W, ldw, C, ldc, bias, M, N, K);

@@ -761,6 +761,11 @@ def seq_moe_route(logits, n_groups, keep, top, scale):
     return ids, wts
 
 
+# entries (tokens x choices) from which a bf16 step runs every expert's rows through the tcgen05 GEMM core (the segment
+# sizes are then read back once per layer); smaller steps, and fp32, stay on the grouped SIMT kernels without a host read
+MOE_DENSE_MIN_ENTRIES = 2048
+
+
 def seq_moe_experts(x, ids, w_gate_up, w_down):
     """x act [n_tok, C]; ids int32 [n_tok, top]; w_gate_up act [n_exp, 2*ff, C] (gate rows, then up rows);
     w_down act [n_exp, C, ff] -> (z fp32 [n_tok*top, C] expert outputs in sorted order, pos_of int32 [n_tok*top])."""
@@ -770,16 +775,32 @@ def seq_moe_experts(x, ids, w_gate_up, w_down):
     ff = ff2 // 2
     n_ent = n_tok * top
     max_tiles = (n_ent + L.llark_seq_moe_tile_rows() - 1) // L.llark_seq_moe_tile_rows() + n_exp
-    ints = torch.empty(2 * n_ent + 3 * max_tiles + 1, device=x.device, dtype=torch.int32)
+    ints = torch.empty(2 * n_ent + 3 * max_tiles + 1 + n_exp + 1, device=x.device, dtype=torch.int32)
     perm, pos_of = ints[:n_ent], ints[n_ent:2 * n_ent]
-    tiles, meta = ints[2 * n_ent:2 * n_ent + 3 * max_tiles], ints[2 * n_ent + 3 * max_tiles:]
-    check(L.llark_seq_moe_sort(_p(ids), n_ent, n_exp, _p(perm), _p(pos_of), _p(tiles), _p(meta), _stream()),
+    tiles, meta = ints[2 * n_ent:2 * n_ent + 3 * max_tiles], ints[2 * n_ent + 3 * max_tiles:2 * n_ent + 3 * max_tiles + 1]
+    seg_off = ints[2 * n_ent + 3 * max_tiles + 1:]
+    check(L.llark_seq_moe_sort(_p(ids), n_ent, n_exp, _p(perm), _p(pos_of), _p(tiles), _p(meta), _p(seg_off), _stream()),
           "seq_moe_sort")
-    act = torch.empty((n_ent, ff), device=x.device, dtype=x.dtype)
-    check(L.llark_seq_moe_up(_p(x), x.stride(0), _p(perm), top, _p(w_gate_up), _p(act), _p(tiles), _p(meta), max_tiles, ff,
-                             C, _actf(x.dtype), _stream()), "seq_moe_up")
     z = torch.empty((n_ent, C), device=x.device, dtype=torch.float32)
-    check(L.llark_seq_moe_down(_p(act), _p(w_down), _p(z), _p(tiles), _p(meta), max_tiles, C, ff, _actf(x.dtype),
+    if x.dtype == BF16 and n_ent >= MOE_DENSE_MIN_ENTRIES and C % 8 == 0 and ff % 8 == 0 and C >= 64 and ff >= 64:
+        if not _INITED:
+            init()
+        host_off = seg_off.cpu()  # the one host read of the step's routing: rows per expert
+        off_p = ctypes.c_void_p(host_off.data_ptr())
+        xs = torch.empty((n_ent, C), device=x.device, dtype=x.dtype)
+        check(L.llark_seq_moe_gather(_p(x), x.stride(0), _p(perm), top, _p(xs), n_ent, C, 0, _stream()), "seq_moe_gather")
+        gu = torch.empty((n_ent, ff2), device=x.device, dtype=x.dtype)
+        act = torch.empty((n_ent, ff), device=x.device, dtype=x.dtype)
+        check(L.llark_gemm_segments(_p(xs), C, _p(w_gate_up), _p(gu), ff2, 0, off_p, n_exp, ff2, C, _stream()),
+              "gemm_segments(gate|up)")
+        check(L.llark_seq_silu_mul(_p(gu), _p(act), n_ent, ff, 0, _stream()), "seq_silu_mul")
+        check(L.llark_gemm_segments(_p(act), ff, _p(w_down), _p(z), C, 1, off_p, n_exp, C, ff, _stream()),
+              "gemm_segments(down)")
+        return z, pos_of
+    act = torch.empty((n_ent, ff), device=x.device, dtype=x.dtype)
+    check(L.llark_seq_moe_up(_p(x), x.stride(0), _p(perm), top, _p(w_gate_up), _p(act), _p(tiles), _p(meta), max_tiles,
+                             n_ent, ff, C, _actf(x.dtype), _stream()), "seq_moe_up")
+    check(L.llark_seq_moe_down(_p(act), _p(w_down), _p(z), _p(tiles), _p(meta), max_tiles, n_ent, C, ff, _actf(x.dtype),
                                _stream()), "seq_moe_down")
     return z, pos_of
 
