@@ -55,7 +55,10 @@ int llark_gemm(const void* A, int a_mn_major, long long lda, const void* B, int 
  *   LLARK_EPI_SWIGLU_BWD  acc = d(act) of the down projection's dgrad; a = gu bf16 [M, ld] (gate | up, N apart);
  *                         C[:, c] = dgate, C[:, N + c] = dup (C is dgu [M, ldc >= 2N]); replaces llark_swiglu_bwd
  * Results are bit-identical to the unfused sequences (same bf16 rounding points). */
-enum { LLARK_EPI_NONE = 0, LLARK_EPI_QUICK_GELU = 1, LLARK_EPI_ROPE = 2, LLARK_EPI_SWIGLU_BWD = 3 };
+/*   LLARK_EPI_SEGMENTS    not an epilogue: the rows of A / C come in runs that each multiply their own block of B (stacked
+ *                         [i1, N, K]); a = device int triples (block, first row, rows <= 256), i0 = their number. Used by
+ *                         llark_gemm_segments. */
+enum { LLARK_EPI_NONE = 0, LLARK_EPI_QUICK_GELU = 1, LLARK_EPI_ROPE = 2, LLARK_EPI_SWIGLU_BWD = 3, LLARK_EPI_SEGMENTS = 4 };
 typedef struct LlarkGemmEpilogue {
     int kind;
     const void* a;
@@ -382,7 +385,8 @@ int llark_seq_head_linear(const void* x, int x_fp32, long long ldx, int x_hs, co
 int llark_seq_tanh(const float* u, void* y, long long n, int act_fp32, cudaStream_t stream);
 /* C[off[e] .. off[e+1]) = A[same rows] @ B[e]^T, e < n_seg; B bf16 [n_seg, N, K]; seg_off_host on the host */
 int llark_gemm_segments(const void* A, long long lda, const void* B, void* C, long long ldc, int c_fp32,
-                        const int* seg_off_host, int n_seg, int N, int K, cudaStream_t stream);
+                        const int* seg_off_host, int n_seg, const int* seg_tiles_dev, int n_tiles, int N, int K,
+                        cudaStream_t stream);
 /* routed mixture of experts (see csrc/seq_moe.cu) */
 int llark_seq_moe_route(const float* logits, long long ld, int* ids, float* wts, int n_tok, int n_exp, int n_groups,
                         int keep, int top, float scale, cudaStream_t stream);

@@ -171,7 +171,7 @@ def lib():
             "llark_seq_silu_mul": ([P, P, LL, I, I, P], I),
             "llark_seq_moe_up": ([P, LL, P, I, P, P, P, P, I, I, I, I, I, P], I),
             "llark_seq_moe_down": ([P, P, P, P, P, I, I, I, I, I, P], I),
-            "llark_gemm_segments": ([P, LL, P, P, LL, I, P, I, I, I, P], I),
+            "llark_gemm_segments": ([P, LL, P, P, LL, I, P, I, P, I, I, I, P], I),
             "llark_seq_tanh": ([P, P, LL, I, P], I),
         }
         for name, (argtypes, restype) in sig.items():

@@ -68,6 +68,9 @@ struct GemmParams {
     const void* epi_b;
     long long epi_ld;
     int epi_i0, epi_i1;
+    // rows-in-runs mode (CTA-pair kernel, K-major bf16 operands): m-block i covers rows seg_tiles[3i+1] .. + seg_tiles[3i+2]
+    // of A / C and multiplies weight block seg_tiles[3i] of B (stacked [blocks, N, K]); nullptr: one matrix
+    const int* seg_tiles;
 };
 
 __device__ __forceinline__ void ld8_bf16(const __nv_bfloat16* ptr, float (&f)[8]) {
@@ -475,11 +478,11 @@ __device__ __forceinline__ void epi_staged_bf16(const GemmParams& p, long long r
 // behind the next tile's MMAs, and the staging patch's extra 256 KB of shared-memory traffic per tile slows the operand
 // pipeline by 3-8 % (profiles/r2c_epilogue_ab.md, profiles/r2k_epilogue_probe.md).
 template <int EPI>
-__device__ __forceinline__ void epilogue_dispatch(const GemmParams& p, long long row0, int lane, int ncol0, uint32_t taddr,
-                                                  float* stg) {
+__device__ __forceinline__ void epilogue_dispatch(const GemmParams& p, long long row0, long long m_end, int lane, int ncol0,
+                                                  uint32_t taddr, float* stg) {
     if ((EPI == 2 && ncol0 < p.epi_i1) || !p.staged) {
         const long long row = row0 + lane;
-        epilogue_tile<EPI>(p, row, row < p.M, ncol0, taddr);
+        epilogue_tile<EPI>(p, row, row < m_end, ncol0, taddr);
         return;
     }
     if (p.c_fp32) {
@@ -628,7 +631,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
             mbar_wait(&tmem_full[as], aphase);
             tc_fence_after();
             const long long row0 = (long long)tc.m_blk * BLOCK_M + ew * 32;
-            epilogue_dispatch<EPI>(p, row0, lane, tc.n_blk * BLOCK_N, tmem_base + ((uint32_t)(ew * 32) << 16) + as * BLOCK_N,
+            epilogue_dispatch<EPI>(p, row0, p.M, lane, tc.n_blk * BLOCK_N, tmem_base + ((uint32_t)(ew * 32) << 16) + as * BLOCK_N,
                                    epi_stage + ew * (EPI_WARP_BYTES / 4));
             tc_fence_before();
             __syncwarp();
@@ -781,8 +784,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         uint32_t phase = 0;
         for (int tile = next_tile(false); tile >= 0; tile = next_tile(false)) {
             const TileCoord tc = tile_coord(tile, p.num_m_blocks, p.num_n_blocks, p.group_m);
-            const int m0 = tc.m_blk * 256 + (int)rank * 128;
-            const int n0 = tc.n_blk * BLOCK_N + (int)rank * 128;
+            const int m0 = (p.seg_tiles ? p.seg_tiles[3 * tc.m_blk + 1] : tc.m_blk * 256) + (int)rank * 128;
+            const int n0 = tc.n_blk * BLOCK_N + (int)rank * 128 + (p.seg_tiles ? p.seg_tiles[3 * tc.m_blk] * p.N : 0);
             const int m_chunk = m0 / mn_per_box, n_chunk = n0 / mn_per_box;  // once per tile, not per stage
             int k0 = 0;
             for (int kb = 0; kb < p.num_k_blocks; ++kb, k0 += elems_per_row) {
@@ -895,8 +898,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
             const uint32_t aphase = (it >> 1) & 1;
             mbar_wait(&tmem_full[as], aphase);
             tc_fence_after();
-            const long long row0 = (long long)tc.m_blk * 256 + (long long)rank * 128 + ew * 32;
-            epilogue_dispatch<EPI>(p, row0, lane, tc.n_blk * BLOCK_N, tmem_base + ((uint32_t)(ew * 32) << 16) + as * BLOCK_N,
+            const long long mbase = p.seg_tiles ? p.seg_tiles[3 * tc.m_blk + 1] : (long long)tc.m_blk * 256;
+            const long long m_end = p.seg_tiles ? mbase + p.seg_tiles[3 * tc.m_blk + 2] : (long long)p.M;
+            const long long row0 = mbase + (long long)rank * 128 + ew * 32;
+            epilogue_dispatch<EPI>(p, row0, m_end, lane, tc.n_blk * BLOCK_N, tmem_base + ((uint32_t)(ew * 32) << 16) + as * BLOCK_N,
                                    epi_stage + ew * (EPI_WARP_BYTES / 4));
             tc_fence_before();
             __syncwarp();
@@ -1171,7 +1176,13 @@ extern "C" int llark_gemm_ex(const void* A, int a_mn_major, long long lda, const
                              const void* R, long long ldr, int M, int N, int K, int in_fp32, int max_ctas,
                              const LlarkGemmEpilogue* ep, cudaStream_t stream) {
     if (M <= 0 || N <= 0 || K <= 0 || !A || !B || !C) return LLARK_EINVAL;
-    if (ep && ep->kind != LLARK_EPI_NONE) {
+    const bool segs = ep && ep->kind == LLARK_EPI_SEGMENTS;
+    if (segs) {
+        // a = device tile list, i0 = its length, i1 = weight blocks stacked in B; plain output otherwise
+        if (!ep->a || ep->i0 <= 0 || ep->i1 <= 0 || a_mn_major || b_mn_major || in_fp32 || bias || R ||
+            !llark_gemm_get_mode())
+            return LLARK_EINVAL;
+    } else if (ep && ep->kind != LLARK_EPI_NONE) {
         switch (ep->kind) {
             case LLARK_EPI_QUICK_GELU:
                 if (R) return LLARK_EINVAL;
@@ -1232,7 +1243,8 @@ extern "C" int llark_gemm_ex(const void* A, int a_mn_major, long long lda, const
     else if (b4)
         rc = get_tensor_map_mn4(&tb, B, N, K, ldb, 2, epr / 8, eb);
     else if (!b_mn_major)
-        rc = get_tensor_map(&tb, B, K, N, ldb, epr, dbg_split ? 64 : (llark_gemm_get_mode() ? 128 : BLOCK_N), eb);
+        rc = get_tensor_map(&tb, B, K, segs ? N * ep->i1 : N, ldb, epr,
+                            dbg_split ? 64 : (llark_gemm_get_mode() ? 128 : BLOCK_N), eb);
     else
         rc = get_tensor_map(&tb, B, N, K, ldb, epr, epr, eb);
     if (rc != LLARK_OK) return rc;
@@ -1254,7 +1266,9 @@ extern "C" int llark_gemm_ex(const void* A, int a_mn_major, long long lda, const
     }
     p.a_tma4 = a4 ? use4 : 0;
     p.b_tma4 = b4 ? use4 : 0;
-    p.epi = ep ? ep->kind : 0;
+    p.epi = (ep && !segs) ? ep->kind : 0;
+    p.seg_tiles = segs ? static_cast<const int*>(ep->a) : nullptr;
+    if (segs) p.num_m_blocks = ep->i0;
     {
         static int mode = -1;  // LLARK_GEMM_EPILOGUE = auto (default) | staged | direct
         if (mode < 0) {
@@ -1268,7 +1282,7 @@ extern "C" int llark_gemm_ex(const void* A, int a_mn_major, long long lda, const
         const bool short_k = (long long)K * eb < 2400LL * 2;  // fewer than ~2400 bf16-equivalent K elements
         const bool want = p.epi == LLARK_EPI_SWIGLU_BWD || (R != nullptr && (c_fp32 || short_k)) ||
                           (c_fp32 && R == nullptr && short_k);
-        p.staged = mode == 1 ? 1 : (mode == 2 ? 0 : (want ? 1 : 0));
+        p.staged = segs ? 0 : (mode == 1 ? 1 : (mode == 2 ? 0 : (want ? 1 : 0)));
     }
     {
         // Rasterisation group: tiles sweep n inside groups of `group_m` m-blocks, so a group's A panel
@@ -1357,10 +1371,23 @@ extern "C" void llark_gemm_clear_cache(void) {
 
 // Runs of rows that each multiply their own weight block: C[off[e] .. off[e+1]) = A[same rows] @ B[e]^T for e < n_seg, with
 // B [n_seg, N, K] stacked and the run boundaries on the host (a routed feed-forward after its rows have been sorted by
-// expert). One call instead of n_seg trips through the language binding; bf16 operands, bf16 or fp32 output.
+// expert). With a device tile list (triples: block, first row, rows <= 256, covering every run) and the CTA-pair kernel
+// this is ONE launch whose m-blocks follow the list; otherwise one launch per run. bf16 operands, bf16 or fp32 output.
 extern "C" int llark_gemm_segments(const void* A, long long lda, const void* B, void* C, long long ldc, int c_fp32,
-                                   const int* seg_off_host, int n_seg, int N, int K, cudaStream_t stream) {
+                                   const int* seg_off_host, int n_seg, const int* seg_tiles_dev, int n_tiles, int N, int K,
+                                   cudaStream_t stream) {
     if (!A || !B || !C || !seg_off_host || n_seg <= 0 || N <= 0 || K <= 0) return LLARK_EINVAL;
+    if (seg_tiles_dev && n_tiles > 0 && llark_gemm_get_mode()) {
+        LlarkGemmEpilogue ep;
+        ep.kind = LLARK_EPI_SEGMENTS;
+        ep.a = seg_tiles_dev;
+        ep.b = nullptr;
+        ep.ld = 0;
+        ep.i0 = n_tiles;
+        ep.i1 = n_seg;
+        return llark_gemm_ex(A, 0, lda, B, 0, K, C, ldc, c_fp32, nullptr, 0, nullptr, 0, seg_off_host[n_seg], N, K, 0, 0, &ep,
+                             stream);
+    }
     const char* a = static_cast<const char*>(A);
     const char* b = static_cast<const char*>(B);
     char* c = static_cast<char*>(C);

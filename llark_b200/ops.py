@@ -787,15 +787,19 @@ def seq_moe_experts(x, ids, w_gate_up, w_down):
             init()
         host_off = seg_off.cpu()  # the one host read of the step's routing: rows per expert
         off_p = ctypes.c_void_p(host_off.data_ptr())
+        off = host_off.tolist()
+        t256 = [v for e in range(n_exp) for r in range(off[e], off[e + 1], 256) for v in (e, r, min(256, off[e + 1] - r))]
+        t256_dev = torch.tensor(t256, dtype=torch.int32).pin_memory().to(x.device, non_blocking=True)
+        n256 = len(t256) // 3
         xs = torch.empty((n_ent, C), device=x.device, dtype=x.dtype)
         check(L.llark_seq_moe_gather(_p(x), x.stride(0), _p(perm), top, _p(xs), n_ent, C, 0, _stream()), "seq_moe_gather")
         gu = torch.empty((n_ent, ff2), device=x.device, dtype=x.dtype)
         act = torch.empty((n_ent, ff), device=x.device, dtype=x.dtype)
-        check(L.llark_gemm_segments(_p(xs), C, _p(w_gate_up), _p(gu), ff2, 0, off_p, n_exp, ff2, C, _stream()),
-              "gemm_segments(gate|up)")
+        check(L.llark_gemm_segments(_p(xs), C, _p(w_gate_up), _p(gu), ff2, 0, off_p, n_exp, _p(t256_dev), n256, ff2, C,
+                                    _stream()), "gemm_segments(gate|up)")
         check(L.llark_seq_silu_mul(_p(gu), _p(act), n_ent, ff, 0, _stream()), "seq_silu_mul")
-        check(L.llark_gemm_segments(_p(act), ff, _p(w_down), _p(z), C, 1, off_p, n_exp, C, ff, _stream()),
-              "gemm_segments(down)")
+        check(L.llark_gemm_segments(_p(act), ff, _p(w_down), _p(z), C, 1, off_p, n_exp, _p(t256_dev), n256, C, ff,
+                                    _stream()), "gemm_segments(down)")
         return z, pos_of
     act = torch.empty((n_ent, ff), device=x.device, dtype=x.dtype)
     check(L.llark_seq_moe_up(_p(x), x.stride(0), _p(perm), top, _p(w_gate_up), _p(act), _p(tiles), _p(meta), max_tiles,

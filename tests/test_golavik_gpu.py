@@ -378,6 +378,42 @@ def test_routed_experts(dtype, n_tok):
     assert _rel(got, want) < (2e-6 if dtype == F32 else 5e-3)
 
 
+def test_routed_experts_large_step_takes_the_gemm_core():
+    """A bf16 step with thousands of (token, choice) entries sorts its rows by expert and runs every run of rows through
+    the tensor-core GEMM in one launch: runs of unequal length, one shorter than a tile, one empty, tiles that straddle
+    nothing. Against the restatement and against the small-step kernels on the same rows."""
+    from llark_b200 import ops
+    from llark_b200.mixers import RoutedExperts
+
+    C, n_tok = 64, 1500
+    mlp = _moe(6, 2, 3, 2, 72, 1.0)
+    cfg = _cfg([_gd(1, 8, mlp=mlp)], width=C)
+    W = {k.replace("l0.mlp.", "f."): v for k, v in go.random_weights(cfg, 5).items() if k.startswith("l0.mlp.")}
+    W["f.router"][3] = 0.0
+    W["f.router"][3, 0] = -16.0          # expert 3 gets no rows
+    W["f.router"][4] *= 0.05
+    W["f.router"][4, 0] = -1.5           # expert 4 gets few
+    g = torch.Generator().manual_seed(1)
+    h = torch.randn(n_tok, C, generator=g)
+    h[:, 0] = 2.0
+    h = h.to(BF16).to(F64)
+    x, y = torch.randn(n_tok, C, generator=g), torch.randn(n_tok, C, generator=g)
+    ff = RoutedExperts(RoutedExperts.Weights({k: v.to(F32) for k, v in W.items()}, "f.", mlp, C, _dev(), BF16), BF16)
+    assert n_tok * 2 >= ops.MOE_DENSE_MIN_ENTRIES
+    got = ff.residual(x.to(_dev()), y.to(_dev()), h.to(_dev(), BF16))
+    want = x.double() + (y.double() + go.moe(h, W, "f.", mlp))
+    assert _rel(got, want) < 5e-3
+    ids, _ = ff.route(h.to(_dev(), BF16))
+    counts = torch.bincount(ids.flatten().cpu().long(), minlength=6)
+    assert counts[3] == 0 and 0 < counts[4] < 256 and counts.max() > 256
+    old, ops.MOE_DENSE_MIN_ENTRIES = ops.MOE_DENSE_MIN_ENTRIES, 10 ** 9
+    try:
+        small = ff.residual(x.to(_dev()), y.to(_dev()), h.to(_dev(), BF16))
+    finally:
+        ops.MOE_DENSE_MIN_ENTRIES = old
+    assert _rel(got, small) < 5e-3
+
+
 # ------------------------------------------------------------------------------------------------ whole model
 @pytest.mark.parametrize("name", sorted(CONFIGS))
 def test_whole_prompt_and_every_layer(name):
