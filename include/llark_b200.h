@@ -367,7 +367,7 @@ int llark_seq_delta_prep(int rule, const float* q, long long q_ld, const float* 
                          cudaStream_t stream);
 /* S[:, e] = d S[:, e] + p1 (z . S[:, e]) + p2 v[e], o[e] = q . S[:, e] per token; state fp32 [slots, H, D, E] */
 int llark_seq_delta_scan(const float* vec, const float* v, long long v_ld, float* state, float* o, const int* cu,
-                         const int* slot, int n_seq, int H, int D, int E, cudaStream_t stream);
+                         const int* slot, int n_seq, int n_tok, int H, int D, int E, cudaStream_t stream);
 /* per-head RMS norm of x fp32 [n_tok, H, E], times w ([E] shared or [H, E]), times sigmoid(gate) -> ACT */
 int llark_seq_head_norm_gate(const float* x, const float* w, int w_per_head, const float* gate, long long gate_ld,
                              void* out, long long n_tok, int H, int E, float eps, int act_fp32, cudaStream_t stream);

@@ -160,7 +160,7 @@ def lib():
             "llark_seq_residual_combine": ([P, P, P, P, P, I, P, I, I, P], I),
             "llark_seq_conv_act": ([P, LL, P, P, P, P, P, P, I, I, I, I, I, P], I),
             "llark_seq_delta_prep": ([I, P, LL, P, LL, P, LL, P, P, P, LL, P, I, I, I, I, F, P], I),
-            "llark_seq_delta_scan": ([P, P, LL, P, P, P, P, I, I, I, I, P], I),
+            "llark_seq_delta_scan": ([P, P, LL, P, P, P, P, I, I, I, I, I, P], I),
             "llark_seq_head_norm_gate": ([P, P, I, P, LL, P, LL, I, I, F, I, P], I),
             "llark_seq_latent_prep": ([P, LL, P, LL, P, P, I, F, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P], I),
             "llark_seq_head_linear": ([P, I, LL, I, P, P, LL, I, P, LL, I, I, I, I, I, P], I),

@@ -135,7 +135,7 @@ __global__ void delta_prep_kernel(int rule, const float* __restrict__ q, long lo
 }
 
 // ------------------------------------------------------------------------------------------------ the recurrence
-// Block per (column slice, head, request). R adjacent lanes share column e of S; lane r owns the 4-row groups r, r + R,
+// Block per (column slice, head, request). R adjacent lanes share CPT adjacent columns of S; lane r owns the 4-row groups r, r + R,
 // r + 2R, ... (rows 4 (r + R i) + c) in registers, so that the R lanes read adjacent 16-byte pieces of a vector (no bank
 // conflicts; lanes of other columns get the same words by broadcast), and the partial sums over rows are added by shuffle. The vectors and values of TS tokens are brought to
 // shared memory with cp.async while the previous TS are computed. Rows d >= D are zero padding (DPT * R >= D).
@@ -150,28 +150,28 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-template <int DPT>
+template <int DPT, int CPT, int R>
 __global__ void __launch_bounds__(256, 1)
 delta_scan_kernel(const float* __restrict__ vec, const float* __restrict__ v, long long v_ld, float* __restrict__ state,
                   float* __restrict__ o, const int* __restrict__ cu, const int* __restrict__ slot, int H, int D, int E,
-                  int R, int cols, int ts) {
+                  int cols, int ts) {
     extern __shared__ __align__(16) float sm[];
-    const int Dp = DPT * R;
+    constexpr int Dp = DPT * R;
     const int stage_floats = ts * (5 * Dp + cols);
     const int h = blockIdx.y, b = blockIdx.z;
-    const int col = threadIdx.x / R, r = threadIdx.x % R;
+    const int cg = threadIdx.x / R, r = threadIdx.x % R;  // column group (CPT adjacent columns), lane within it
     const int e0 = blockIdx.x * cols;
-    const int e = e0 + col;
+    const int ec = e0 + cg * CPT;                         // first column of this thread
     const int row0 = cu[b], n = cu[b + 1] - row0;
-    const bool live = e < E;
-    float S[DPT];
+    float S[CPT][DPT];
     float* sp = state + (((long long)slot[b] * H + h) * D) * E;
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
         const int d = 4 * (r + R * (i >> 2)) + (i & 3);
-        S[i] = (live && d < D) ? sp[(long long)d * E + e] : 0.f;
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) S[c][i] = (ec + c < E && d < D) ? sp[(long long)d * E + ec + c] : 0.f;
     }
-    for (int i = threadIdx.x; i < 2 * stage_floats; i += blockDim.x) sm[i] = 0.f;  // padding rows stay zero
+    for (int i = threadIdx.x; i < 2 * stage_floats; i += blockDim.x) sm[i] = 0.f;  // padding rows / columns stay zero
     __syncthreads();
     const bool vec16 = (D % 4) == 0;
     auto issue = [&](int tok0, int st) {
@@ -225,41 +225,72 @@ delta_scan_kernel(const float* __restrict__ vec, const float* __restrict__ v, lo
             const float4* pd = reinterpret_cast<const float4*>(base + (tk * 5 + 2) * Dp) + r;
             const float4* p1 = reinterpret_cast<const float4*>(base + (tk * 5 + 3) * Dp) + r;
             const float4* p2 = reinterpret_cast<const float4*>(base + (tk * 5 + 4) * Dp) + r;
-            float z0 = 0.f, z1 = 0.f, z2 = 0.f, z3 = 0.f;  // four chains instead of one
+            // z . S of every column: every vector word loaded once for CPT columns, CPT independent chains (two each when
+            // the thread has one column only)
+            float zs[CPT], zt[CPT];
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) zs[c] = zt[c] = 0.f;
 #pragma unroll
             for (int i = 0; i < DPT / 4; ++i) {
                 const float4 z = pz[R * i];
-                z0 = fmaf(z.x, S[4 * i], z0);
-                z1 = fmaf(z.y, S[4 * i + 1], z1);
-                z2 = fmaf(z.z, S[4 * i + 2], z2);
-                z3 = fmaf(z.w, S[4 * i + 3], z3);
+#pragma unroll
+                for (int c = 0; c < CPT; ++c) {
+                    zs[c] = fmaf(z.x, S[c][4 * i], zs[c]);
+                    zt[c] = fmaf(z.y, S[c][4 * i + 1], zt[c]);
+                    zs[c] = fmaf(z.z, S[c][4 * i + 2], zs[c]);
+                    zt[c] = fmaf(z.w, S[c][4 * i + 3], zt[c]);
+                }
             }
-            float zs = (z0 + z1) + (z2 + z3);
-            for (int m = 1; m < R; m <<= 1) zs += __shfl_xor_sync(0xffffffffu, zs, m);
-            const float vv = sv[tk * cols + col];
-            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) zs[c] += zt[c];
+#pragma unroll
+            for (int m = 1; m < R; m <<= 1) {
+#pragma unroll
+                for (int c = 0; c < CPT; ++c) zs[c] += __shfl_xor_sync(0xffffffffu, zs[c], m);
+            }
+            float vv[CPT], os[CPT], ot[CPT];
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) {
+                vv[c] = sv[tk * cols + cg * CPT + c];
+                os[c] = ot[c] = 0.f;
+            }
 #pragma unroll
             for (int i = 0; i < DPT / 4; ++i) {
-                const float4 dd = pd[R * i], a = p1[R * i], c = p2[R * i], qq = pq[R * i];
-                S[4 * i] = fmaf(c.x, vv, fmaf(a.x, zs, dd.x * S[4 * i]));
-                S[4 * i + 1] = fmaf(c.y, vv, fmaf(a.y, zs, dd.y * S[4 * i + 1]));
-                S[4 * i + 2] = fmaf(c.z, vv, fmaf(a.z, zs, dd.z * S[4 * i + 2]));
-                S[4 * i + 3] = fmaf(c.w, vv, fmaf(a.w, zs, dd.w * S[4 * i + 3]));
-                o0 = fmaf(qq.x, S[4 * i], o0);
-                o1 = fmaf(qq.y, S[4 * i + 1], o1);
-                o2 = fmaf(qq.z, S[4 * i + 2], o2);
-                o3 = fmaf(qq.w, S[4 * i + 3], o3);
+                const float4 dd = pd[R * i], a = p1[R * i], w2 = p2[R * i], qq = pq[R * i];
+#pragma unroll
+                for (int c = 0; c < CPT; ++c) {
+                    S[c][4 * i] = fmaf(w2.x, vv[c], fmaf(a.x, zs[c], dd.x * S[c][4 * i]));
+                    S[c][4 * i + 1] = fmaf(w2.y, vv[c], fmaf(a.y, zs[c], dd.y * S[c][4 * i + 1]));
+                    S[c][4 * i + 2] = fmaf(w2.z, vv[c], fmaf(a.z, zs[c], dd.z * S[c][4 * i + 2]));
+                    S[c][4 * i + 3] = fmaf(w2.w, vv[c], fmaf(a.w, zs[c], dd.w * S[c][4 * i + 3]));
+                    os[c] = fmaf(qq.x, S[c][4 * i], os[c]);
+                    ot[c] = fmaf(qq.y, S[c][4 * i + 1], ot[c]);
+                    os[c] = fmaf(qq.z, S[c][4 * i + 2], os[c]);
+                    ot[c] = fmaf(qq.w, S[c][4 * i + 3], ot[c]);
+                }
             }
-            float os = (o0 + o1) + (o2 + o3);
-            for (int m = 1; m < R; m <<= 1) os += __shfl_xor_sync(0xffffffffu, os, m);
-            if (r == 0 && live) o[(long long)(row0 + tok0 + tk) * H * E + (long long)h * E + e] = os;
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) os[c] += ot[c];
+#pragma unroll
+            for (int m = 1; m < R; m <<= 1) {
+#pragma unroll
+                for (int c = 0; c < CPT; ++c) os[c] += __shfl_xor_sync(0xffffffffu, os[c], m);
+            }
+            if (r == 0) {
+                float* orow = o + (long long)(row0 + tok0 + tk) * H * E + (long long)h * E + ec;
+#pragma unroll
+                for (int c = 0; c < CPT; ++c)
+                    if (ec + c < E) orow[c] = os[c];
+            }
         }
         __syncthreads();
     }
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
         const int d = 4 * (r + R * (i >> 2)) + (i & 3);
-        if (live && d < D) sp[(long long)d * E + e] = S[i];
+#pragma unroll
+        for (int c = 0; c < CPT; ++c)
+            if (ec + c < E && d < D) sp[(long long)d * E + ec + c] = S[c][i];
     }
 }
 
@@ -322,26 +353,60 @@ extern "C" int llark_seq_delta_prep(int rule, const float* q, long long q_ld, co
 }
 
 extern "C" int llark_seq_delta_scan(const float* vec, const float* v, long long v_ld, float* state, float* o,
-                                    const int* cu, const int* slot, int n_seq, int H, int D, int E, cudaStream_t st) {
-    if (n_seq <= 0 || H <= 0 || D <= 0 || E <= 0 || !vec || !v || !state || !o || !cu || !slot) return LLARK_EINVAL;
-    constexpr int DPT = 32;
-    if (D > 8 * DPT) return LLARK_EINVAL;
-    int R = 1;
-    while (R * DPT < D) R <<= 1;
-    // columns per block: enough blocks to fill the GPU at small batches, full warps, at most 256 threads
-    int cols = 256 / R;
-    const int min_cols = 32 / R > 8 ? 32 / R : 8;
-    while (cols > min_cols && (long long)((E + cols - 1) / cols) * H * n_seq < 2 * 148) cols >>= 1;
-    while (cols > min_cols && cols / 2 >= E) cols >>= 1;
-    const int ts = D <= 128 ? 8 : 4;
-    const size_t smem = sizeof(float) * 2 * (size_t)ts * (5 * DPT * R + cols);
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaFuncSetAttribute(delta_scan_kernel<DPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-        attr_set = true;
+                                    const int* cu, const int* slot, int n_seq, int n_tok, int H, int D, int E,
+                                    cudaStream_t st) {
+    if (n_seq <= 0 || n_tok < n_seq || H <= 0 || D <= 0 || E <= 0 || !vec || !v || !state || !o || !cu || !slot)
+        return LLARK_EINVAL;
+    // 16 rows of a column per thread (short dependent chains) while a column then still fits one warp, 32 rows for the
+    // widest heads. Steps with many tokens per request give a thread two adjacent columns: a vector word read from
+    // shared memory then serves both (the shared-memory pipe is what bounds the one-column form on prompts);
+    // single-token steps keep one column per thread, which reads and writes the state in whole rows.
+    const int dpt = D <= 16 * 32 ? 16 : 32;
+    if (D > 32 * 32) return LLARK_EINVAL;
+    int cpt = (dpt == 16 && n_tok >= 16 * n_seq && E >= 4) ? 2 : 1;
+    {
+        static int forced = -1;  // LLARK_DELTA_CPT = 1 | 2 | 4: columns per thread on long steps (measurement aid)
+        if (forced < 0) {
+            const char* e = getenv("LLARK_DELTA_CPT");
+            forced = e ? atoi(e) : 0;
+        }
+        if (cpt == 2 && (forced == 1 || forced == 4)) cpt = forced;
     }
+    int R = 1;
+    while (R * dpt < D) R <<= 1;
+    // columns per block: enough blocks to fill the GPU at small batches, at least two warps, at most 256 threads
+    const int floor_cols = cpt * (64 / R > 1 ? 64 / R : 1) > 8 ? cpt * (64 / R > 1 ? 64 / R : 1) : 8;
+    int cols = cpt * (256 / R > 1 ? 256 / R : 1);
+    if (cols < floor_cols) cols = floor_cols;
+    while (cols > floor_cols && (long long)((E + cols - 1) / cols) * H * n_seq < 2 * 148) cols >>= 1;
+    while (cols > floor_cols && cols / 2 >= E) cols >>= 1;
+    const int threads = cols / cpt * R;
+    if (threads % 32 || threads > 256) return LLARK_EINVAL;
+    const int ts = D <= 128 ? 8 : (D <= 256 ? 4 : (D <= 512 ? 2 : 1));  // two stages stay under 48 KB
+    const size_t smem = sizeof(float) * 2 * (size_t)ts * (5 * dpt * R + cols);
     dim3 grid((E + cols - 1) / cols, H, n_seq);
-    delta_scan_kernel<DPT><<<grid, cols * R, smem, st>>>(vec, v, v_ld, state, o, cu, slot, H, D, E, R, cols, ts);
+#define LLARK_DSCAN(DPT_, CPT_, R_)                                                                                   \
+    delta_scan_kernel<DPT_, CPT_, R_><<<grid, threads, smem, st>>>(vec, v, v_ld, state, o, cu, slot, H, D, E, cols, ts)
+#define LLARK_DSCAN_R(DPT_, CPT_)                                                                                     \
+    switch (R) {                                                                                                      \
+        case 1: LLARK_DSCAN(DPT_, CPT_, 1); break;                                                                    \
+        case 2: LLARK_DSCAN(DPT_, CPT_, 2); break;                                                                    \
+        case 4: LLARK_DSCAN(DPT_, CPT_, 4); break;                                                                    \
+        case 8: LLARK_DSCAN(DPT_, CPT_, 8); break;                                                                    \
+        case 16: LLARK_DSCAN(DPT_, CPT_, 16); break;                                                                  \
+        default: LLARK_DSCAN(DPT_, CPT_, 32); break;                                                                  \
+    }
+    if (dpt == 32) {
+        LLARK_DSCAN(32, 1, 32);  // 512 < D <= 1024
+    } else if (cpt == 4) {
+        LLARK_DSCAN_R(16, 4)
+    } else if (cpt == 2) {
+        LLARK_DSCAN_R(16, 2)
+    } else {
+        LLARK_DSCAN_R(16, 1)
+    }
+#undef LLARK_DSCAN_R
+#undef LLARK_DSCAN
     return check_launch();
 }
 

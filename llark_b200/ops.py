@@ -712,8 +712,8 @@ def seq_delta_scan(vec, v, state, st, H, D, E):
     o fp32 [n_tok, H*E]."""
     _req(vec, torch.float32), _req(v, torch.float32), _req(state, torch.float32)
     o = torch.empty((st.n_tok, H * E), device=v.device, dtype=torch.float32)
-    check(lib().llark_seq_delta_scan(_p(vec), _p(v), v.stride(0), _p(state), _p(o), _p(st.cu), _p(st.slot), st.n_seq, H,
-                                     D, E, _stream()), "seq_delta_scan")
+    check(lib().llark_seq_delta_scan(_p(vec), _p(v), v.stride(0), _p(state), _p(o), _p(st.cu), _p(st.slot), st.n_seq,
+                                     st.n_tok, H, D, E, _stream()), "seq_delta_scan")
     return o
 
 

@@ -203,7 +203,8 @@ def _scan(rule, q, k, v, dec, mix, H, G, D, E, portions, dec_bias=None, rate_log
     return torch.cat(outs), state[slot].cpu()
 
 
-@pytest.mark.parametrize("H,G,D,E", [(4, 2, 8, 12), (3, 1, 10, 7), (2, 2, 64, 64), (1, 1, 144, 40), (2, 1, 256, 16)])
+@pytest.mark.parametrize("H,G,D,E", [(4, 2, 8, 12), (3, 1, 10, 7), (2, 2, 64, 64), (1, 1, 144, 40), (2, 1, 256, 16),
+                                     (1, 1, 400, 3), (1, 1, 640, 9)])
 def test_gated_delta_scan(H, G, D, E):
     from llark_b200 import ops
 
