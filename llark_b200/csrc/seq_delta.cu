@@ -66,6 +66,44 @@ __global__ void conv_act_kernel(const float* __restrict__ src, long long ld, con
     }
 }
 
+// Prompts: a thread walks TB consecutive rows of one channel with the last TAPS-1 inputs in registers, so every input is
+// read once (the per-row kernel reads it TAPS times) and the accesses of a warp are adjacent channels of one row. The
+// window is rebuilt wherever a request starts inside the run of rows.
+template <int TAPS, int TB>
+__global__ void conv_act_rows_kernel(const float* __restrict__ src, long long ld, const float* __restrict__ w,
+                                     const float* __restrict__ carry, const int* __restrict__ tok_seq,
+                                     const int* __restrict__ cu, const int* __restrict__ slot, float* __restrict__ out,
+                                     int n_tok, int n_ch, int silu) {
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= n_ch) return;
+    const int t0 = blockIdx.x * TB;
+    float wr[TAPS], win[TAPS > 1 ? TAPS - 1 : 1];
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) wr[j] = w[(long long)c * TAPS + j];
+    for (int i = 0; i < TB && t0 + i < n_tok; ++i) {
+        const int t = t0 + i;
+        const int b = tok_seq[t];
+        const int local = t - cu[b];
+        if (i == 0 || local < TAPS - 1) {
+            const float* cr = carry + (long long)slot[b] * (TAPS - 1) * n_ch;
+#pragma unroll
+            for (int j = 0; j < TAPS - 1; ++j) {
+                const int s = local - (TAPS - 1) + j;
+                win[j] = s >= 0 ? src[(long long)(t - local + s) * ld + c] : cr[(long long)(TAPS - 1 + s) * n_ch + c];
+            }
+        }
+        const float cur = src[(long long)t * ld + c];
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < TAPS - 1; ++j) acc = fmaf(wr[j], win[j], acc);
+        acc = fmaf(wr[TAPS - 1], cur, acc);
+        out[(long long)t * n_ch + c] = silu ? acc * sigmoidf_(acc) : acc;
+#pragma unroll
+        for (int j = 0; j + 1 < TAPS - 1; ++j) win[j] = win[j + 1];
+        if (TAPS > 1) win[TAPS - 2] = cur;
+    }
+}
+
 // new carry[k] = input at local index n - (taps-1) + k: a row of this step, or an older carry entry when negative
 __global__ void conv_carry_kernel(const float* __restrict__ src, long long ld, float* __restrict__ carry,
                                   const int* __restrict__ cu, const int* __restrict__ slot, int n_ch, int taps) {
@@ -333,7 +371,18 @@ extern "C" int llark_seq_conv_act(const float* src, long long ld, const float* w
     int th = 32;
     while (th < n_ch && th < 256) th <<= 1;
     const int inline_carry = n_tok == n_seq;  // every request brings one token
-    conv_act_kernel<<<n_tok, th, 0, st>>>(src, ld, w, carry, tok_seq, cu, slot, out, n_ch, taps, silu, inline_carry);
+    if (!inline_carry && n_tok >= 64 && taps >= 2 && taps <= 4) {
+        constexpr int TB = 16;
+        dim3 grid((n_tok + TB - 1) / TB, (n_ch + 127) / 128);
+        if (taps == 2)
+            conv_act_rows_kernel<2, TB><<<grid, 128, 0, st>>>(src, ld, w, carry, tok_seq, cu, slot, out, n_tok, n_ch, silu);
+        else if (taps == 3)
+            conv_act_rows_kernel<3, TB><<<grid, 128, 0, st>>>(src, ld, w, carry, tok_seq, cu, slot, out, n_tok, n_ch, silu);
+        else
+            conv_act_rows_kernel<4, TB><<<grid, 128, 0, st>>>(src, ld, w, carry, tok_seq, cu, slot, out, n_tok, n_ch, silu);
+    } else {
+        conv_act_kernel<<<n_tok, th, 0, st>>>(src, ld, w, carry, tok_seq, cu, slot, out, n_ch, taps, silu, inline_carry);
+    }
     int rc = check_launch();
     if (rc != LLARK_OK || inline_carry || taps == 1) return rc;
     conv_carry_kernel<<<n_seq, th, 0, st>>>(src, ld, carry, cu, slot, n_ch, taps);

@@ -320,6 +320,13 @@ class RoutedExpertsWeights:
         if self.n % self.n_groups or not 0 < self.keep <= self.n_groups or self.top > self.keep * (self.n // self.n_groups):
             raise ValueError(f"{pfx}: router groups do not fit experts / top")
         self.router = _vec(w, pfx + "router", dev)  # the router runs in fp32 whatever the serving dtype
+        # A checkpoint stores bf16, so the router's weights usually ARE bf16 numbers. The product of two bf16 numbers is
+        # exact in fp32, so on bf16 activations the tensor-core GEMM with its fp32 accumulator computes the same sums of
+        # exact products as the fp32 kernel does, in another order. Rows padded with zeros to a whole 64-wide tile.
+        self.router_act = None
+        if act == torch.bfloat16 and bool((self.router.to(act).to(F32) == self.router).all()):
+            pad = (-self.n) % 64
+            self.router_act = torch.cat([self.router.to(act), torch.zeros((pad, width), device=dev, dtype=act)]).contiguous()
         self.w_gate_up = torch.stack([torch.cat([_mat(w, f"{pfx}e{e}.gate", dev, act), _mat(w, f"{pfx}e{e}.up", dev, act)])
                                       for e in range(self.n)]).contiguous()
         self.w_down = torch.stack([_mat(w, f"{pfx}e{e}.down", dev, act) for e in range(self.n)]).contiguous()
@@ -336,7 +343,11 @@ class RoutedExperts:
 
     def route(self, x_act):
         w = self.w
-        return ops.seq_moe_route(ops.linear_w32(x_act, w.router), w.n_groups, w.keep, w.top, w.scale)
+        if w.router_act is not None:
+            logits = ops.linear(x_act, w.router_act, out_dtype=F32)[:, :w.n]
+        else:
+            logits = ops.linear_w32(x_act, w.router)
+        return ops.seq_moe_route(logits, w.n_groups, w.keep, w.top, w.scale)
 
     def residual(self, x, y, x_act):
         """x + (y + experts(x_act)): fp32 residual sum with the mixer's output y."""

@@ -164,12 +164,15 @@ def test_conv_act_carries_its_inputs_across_steps(taps):
     C, extra = 37, 5  # the channels are a column slice of a wider matrix
     g = torch.Generator().manual_seed(taps)
     w = torch.randn(C, taps, generator=g)
-    seqs = [torch.randn(60, C + extra, generator=g), torch.randn(31, C + extra, generator=g)]
+    seqs = [torch.randn(60 + 130, C + extra, generator=g), torch.randn(31 + 75, C + extra, generator=g)]
     want = [go.silu(go.causal_conv(s[:, 2:2 + C].double(), w.double())) for s in seqs]
     carry = torch.full((6, max(taps - 1, 1), C), 7.0, device=_dev())
     carry[[4, 1]] = 0.0
     slots = [4, 1]
-    plan = [([5, 2], [0, 1]), ([1, 1], [0, 1]), ([1, 8], [0, 1]), ([2], [0]), ([10, 20], [0, 1]), ([1], [0]), ([40], [0])]
+    # short portions and single tokens (row-per-block kernel), then long ones (the kernel that walks runs of rows: a
+    # request that starts in the middle of a run)
+    plan = [([5, 2], [0, 1]), ([1, 1], [0, 1]), ([1, 8], [0, 1]), ([2], [0]), ([10, 20], [0, 1]), ([1], [0]), ([40], [0]),
+            ([97, 3], [0, 1]), ([33, 72], [0, 1])]
     at, got = [0, 0], [[], []]
     for lens, who in plan:
         st = _layout(lens, [at[b] for b in who], [slots[b] for b in who])
