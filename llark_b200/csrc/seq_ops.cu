@@ -435,6 +435,62 @@ __global__ void group_rmsnorm_kernel(const float* __restrict__ x, const int* __r
     }
 }
 
+// The same with a warp per (row, part) when a part is a whole number of 16-byte pieces: the part stays in registers
+// between the sum of squares and the scaling (up to 1024 elements; longer parts are read twice), no block barrier.
+template <typename T>
+__global__ void group_rmsnorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                                          const float* __restrict__ add_vec, float* __restrict__ x_out,
+                                          const float* __restrict__ w, T* __restrict__ out, int n_rows, int C, int groups,
+                                          float eps) {
+    const int lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (long long)n_rows * groups) return;
+    const long long r = item / groups;
+    const int g = (int)(item % groups);
+    const long long src = rows ? rows[r] : r;
+    const int per = C / groups, nv = per >> 2;
+    const float4* xr = reinterpret_cast<const float4*>(x + src * C + (long long)g * per);
+    const float4* av = add_vec ? reinterpret_cast<const float4*>(add_vec + (long long)g * per) : nullptr;
+    float4 keep[8];
+    float ss = 0.f;
+    auto load = [&](int v) {
+        float4 a = xr[v];
+        if (av) {
+            const float4 b = av[v];
+            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        }
+        return a;
+    };
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int v = lane + 32 * i;
+        if (v < nv) {
+            keep[i] = load(v);
+            ss += keep[i].x * keep[i].x + keep[i].y * keep[i].y + keep[i].z * keep[i].z + keep[i].w * keep[i].w;
+        }
+    }
+    for (int v = lane + 256; v < nv; v += 32) {
+        const float4 a = load(v);
+        ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+    }
+    ss = warp_sum(ss);
+    const float rn = 1.0f / sqrtf(ss / (float)per + eps);
+    const float4* wr = reinterpret_cast<const float4*>(w + (long long)g * per);
+    float4* xo = x_out ? reinterpret_cast<float4*>(x_out + src * C + (long long)g * per) : nullptr;
+    T* orow = out + r * C + (long long)g * per;
+    auto emit = [&](int v, const float4& a) {
+        if (xo) xo[v] = a;
+        const float4 wv = wr[v];
+        st4(orow + 4 * v, make_float4(a.x * rn * wv.x, a.y * rn * wv.y, a.z * rn * wv.z, a.w * rn * wv.w));
+    };
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int v = lane + 32 * i;
+        if (v < nv) emit(v, keep[i]);
+    }
+    for (int v = lane + 256; v < nv; v += 32) emit(v, load(v));
+}
+
 // x_out = x + (y + sum_k wts[t, k] * z[pos_of[t * top + k]]): the residual sum of a layer whose sublayers run side by
 // side, the second one a mixture whose chosen experts' outputs sit in rows pos_of[...] of z (top = 0: no second one).
 __global__ void residual_combine_kernel(const float* __restrict__ x, const float* __restrict__ y,
@@ -656,6 +712,20 @@ extern "C" int llark_seq_group_rmsnorm(const float* x, const int* rows, const fl
                                        cudaStream_t st) {
     if (n_rows <= 0 || C <= 0 || groups <= 0 || (C % groups) || !x || !w || !out) return LLARK_EINVAL;
     if (x_out && rows) return LLARK_EINVAL;
+    const int per = C / groups;
+    const bool al = (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out) |
+                       reinterpret_cast<uintptr_t>(add_vec) | reinterpret_cast<uintptr_t>(x_out)) & 15) == 0);
+    if (per % 4 == 0 && al) {
+        const long long items = (long long)n_rows * groups;
+        const unsigned grid = (unsigned)((items + 3) / 4);
+        if (out_fp32)
+            group_rmsnorm_warp_kernel<float><<<grid, 128, 0, st>>>(x, rows, add_vec, x_out, w, (float*)out, n_rows, C,
+                                                                   groups, eps);
+        else
+            group_rmsnorm_warp_kernel<bf16_t><<<grid, 128, 0, st>>>(x, rows, add_vec, x_out, w, (bf16_t*)out, n_rows, C,
+                                                                    groups, eps);
+        return check_launch();
+    }
     const int th = norm_threads(C / groups * 4);
     if (out_fp32)
         group_rmsnorm_kernel<float><<<n_rows, th, 0, st>>>(x, rows, add_vec, x_out, w, (float*)out, C, groups, eps);

@@ -140,7 +140,7 @@ def _run_mixer(cls, W, spec, width, h, portions, act, eps=1e-5, slot=2):
 
 
 # ------------------------------------------------------------------------------------------------ mechanisms alone
-@pytest.mark.parametrize("groups,C", [(1, 40), (2, 72), (3, 51), (4, 1024)])
+@pytest.mark.parametrize("groups,C", [(1, 40), (2, 72), (3, 51), (4, 1024), (1, 4100), (2, 4096)])
 def test_group_norm(groups, C):
     from llark_b200 import ops
 
