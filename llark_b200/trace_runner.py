@@ -46,7 +46,7 @@ def main(argv=None):
         if not line:
             continue
         step = json.loads(line)
-        entries = step.get("entries", [])
+        entries = [e for e in step.get("entries", []) if e.get("tokens")]  # an entry without tokens asks for nothing
         if entries:
             for e in entries:
                 if e["id"] not in slots:
