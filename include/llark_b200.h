@@ -56,8 +56,8 @@ int llark_gemm(const void* A, int a_mn_major, long long lda, const void* B, int 
  *                         C[:, c] = dgate, C[:, N + c] = dup (C is dgu [M, ldc >= 2N]); replaces llark_swiglu_bwd
  * Results are bit-identical to the unfused sequences (same bf16 rounding points). */
 /*   LLARK_EPI_SEGMENTS    not an epilogue: the rows of A / C come in runs that each multiply their own block of B (stacked
- *                         [i1, N, K]); a = device int triples (block, first row, rows <= 256), i0 = their number. Used by
- *                         llark_gemm_segments. */
+ *                         [i1, N, K]); a = device int triples (block, first row, rows <= 256), i0 = their number (an upper
+ *                         bound when b points at a device word with the real number). Used by llark_gemm_segments. */
 enum { LLARK_EPI_NONE = 0, LLARK_EPI_QUICK_GELU = 1, LLARK_EPI_ROPE = 2, LLARK_EPI_SWIGLU_BWD = 3, LLARK_EPI_SEGMENTS = 4 };
 typedef struct LlarkGemmEpilogue {
     int kind;
@@ -385,14 +385,15 @@ int llark_seq_head_linear(const void* x, int x_fp32, long long ldx, int x_hs, co
 int llark_seq_tanh(const float* u, void* y, long long n, int act_fp32, cudaStream_t stream);
 /* C[off[e] .. off[e+1]) = A[same rows] @ B[e]^T, e < n_seg; B bf16 [n_seg, N, K]; seg_off_host on the host */
 int llark_gemm_segments(const void* A, long long lda, const void* B, void* C, long long ldc, int c_fp32,
-                        const int* seg_off_host, int n_seg, const int* seg_tiles_dev, int n_tiles, int N, int K,
-                        cudaStream_t stream);
+                        const int* seg_off_host, int n_seg, const int* seg_tiles_dev, int n_tiles, const int* seg_count_dev,
+                        int m_total, int N, int K, cudaStream_t stream);
 /* routed mixture of experts (see csrc/seq_moe.cu) */
 int llark_seq_moe_route(const float* logits, long long ld, int* ids, float* wts, int n_tok, int n_exp, int n_groups,
                         int keep, int top, float scale, cudaStream_t stream);
 int llark_seq_moe_tile_rows(void);
+/* meta[0] = number of 64-row tiles; with tiles256: 256-row tiles for llark_gemm_segments, their number in meta[1] */
 int llark_seq_moe_sort(const int* ids, int n_ent, int n_exp, int* perm, int* pos_of, int* tiles, int* meta, int* seg_off,
-                       cudaStream_t stream);
+                       int* tiles256, cudaStream_t stream);
 /* xs[p] = x[perm[p] / top] (rows in sorted order); act = silu(gu[:, :ff]) * gu[:, ff:] */
 int llark_seq_moe_gather(const void* x, long long ldx, const int* perm, int top, void* xs, int n_ent, int C, int act_fp32,
                          cudaStream_t stream);

@@ -166,12 +166,12 @@ def lib():
             "llark_seq_head_linear": ([P, I, LL, I, P, P, LL, I, P, LL, I, I, I, I, I, P], I),
             "llark_seq_moe_route": ([P, LL, P, P, I, I, I, I, I, F, P], I),
             "llark_seq_moe_tile_rows": ([], I),
-            "llark_seq_moe_sort": ([P, I, I, P, P, P, P, P, P], I),
+            "llark_seq_moe_sort": ([P, I, I, P, P, P, P, P, P, P], I),
             "llark_seq_moe_gather": ([P, LL, P, I, P, I, I, I, P], I),
             "llark_seq_silu_mul": ([P, P, LL, I, I, P], I),
             "llark_seq_moe_up": ([P, LL, P, I, P, P, P, P, I, I, I, I, I, P], I),
             "llark_seq_moe_down": ([P, P, P, P, P, I, I, I, I, I, P], I),
-            "llark_gemm_segments": ([P, LL, P, P, LL, I, P, I, P, I, I, I, P], I),
+            "llark_gemm_segments": ([P, LL, P, P, LL, I, P, I, P, I, P, I, I, I, P], I),
             "llark_seq_tanh": ([P, P, LL, I, P], I),
         }
         for name, (argtypes, restype) in sig.items():

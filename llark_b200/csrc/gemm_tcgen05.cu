@@ -71,6 +71,7 @@ struct GemmParams {
     // rows-in-runs mode (CTA-pair kernel, K-major bf16 operands): m-block i covers rows seg_tiles[3i+1] .. + seg_tiles[3i+2]
     // of A / C and multiplies weight block seg_tiles[3i] of B (stacked [blocks, N, K]); nullptr: one matrix
     const int* seg_tiles;
+    const int* seg_count;  // device word: how many entries of seg_tiles are real (num_m_blocks is then an upper bound)
 };
 
 __device__ __forceinline__ void ld8_bf16(const __nv_bfloat16* ptr, float (&f)[8]) {
@@ -683,8 +684,9 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
     const bool leader = rank == 0;
     const int num_clusters = gridDim.x >> 1;
     const int cluster_id = blockIdx.x >> 1;
-    // p.num_m_blocks counts 256-row blocks here
-    const int num_tiles = p.num_m_blocks * p.num_n_blocks;
+    // p.num_m_blocks counts 256-row blocks here; in rows-in-runs mode the real count may live on the device
+    const int num_m_blocks = p.seg_count ? min(*p.seg_count, p.num_m_blocks) : p.num_m_blocks;
+    const int num_tiles = num_m_blocks * p.num_n_blocks;
     const int elems_per_row = BLOCK_KB / kElemBytes;
 
     if (warp == 0 && lane == 0) {
@@ -783,7 +785,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         int stage = 0;
         uint32_t phase = 0;
         for (int tile = next_tile(false); tile >= 0; tile = next_tile(false)) {
-            const TileCoord tc = tile_coord(tile, p.num_m_blocks, p.num_n_blocks, p.group_m);
+            const TileCoord tc = tile_coord(tile, num_m_blocks, p.num_n_blocks, p.group_m);
             const int m0 = (p.seg_tiles ? p.seg_tiles[3 * tc.m_blk + 1] : tc.m_blk * 256) + (int)rank * 128;
             const int n0 = tc.n_blk * BLOCK_N + (int)rank * 128 + (p.seg_tiles ? p.seg_tiles[3 * tc.m_blk] * p.N : 0);
             const int m_chunk = m0 / mn_per_box, n_chunk = n0 / mn_per_box;  // once per tile, not per stage
@@ -893,7 +895,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         int it = 0;
         const uint32_t leader_empty0 = mapa_shared(smem_u32(&tmem_empty[0]), 0);
         for (int tile = next_tile(true); tile >= 0; tile = next_tile(true), ++it) {
-            const TileCoord tc = tile_coord(tile, p.num_m_blocks, p.num_n_blocks, p.group_m);
+            const TileCoord tc = tile_coord(tile, num_m_blocks, p.num_n_blocks, p.group_m);
             const int as = it & 1;
             const uint32_t aphase = (it >> 1) & 1;
             mbar_wait(&tmem_full[as], aphase);
@@ -1268,6 +1270,7 @@ extern "C" int llark_gemm_ex(const void* A, int a_mn_major, long long lda, const
     p.b_tma4 = b4 ? use4 : 0;
     p.epi = (ep && !segs) ? ep->kind : 0;
     p.seg_tiles = segs ? static_cast<const int*>(ep->a) : nullptr;
+    p.seg_count = segs ? static_cast<const int*>(ep->b) : nullptr;
     if (segs) p.num_m_blocks = ep->i0;
     {
         static int mode = -1;  // LLARK_GEMM_EPILOGUE = auto (default) | staged | direct
@@ -1369,25 +1372,28 @@ extern "C" void llark_gemm_clear_cache(void) {
     g_map_cache.clear();
 }
 
-// Runs of rows that each multiply their own weight block: C[off[e] .. off[e+1]) = A[same rows] @ B[e]^T for e < n_seg, with
-// B [n_seg, N, K] stacked and the run boundaries on the host (a routed feed-forward after its rows have been sorted by
-// expert). With a device tile list (triples: block, first row, rows <= 256, covering every run) and the CTA-pair kernel
-// this is ONE launch whose m-blocks follow the list; otherwise one launch per run. bf16 operands, bf16 or fp32 output.
+// Runs of rows that each multiply their own weight block: C[run e] = A[run e] @ B[e]^T for e < n_seg, with B [n_seg, N, K]
+// stacked (a routed feed-forward after its rows have been sorted by expert). With a device tile list (triples: block,
+// first row, rows <= 256, covering every run) and the CTA-pair kernel this is ONE launch whose m-blocks follow the list;
+// n_tiles is the list's length or, with seg_count_dev (a device word holding the real length), an upper bound of it, so
+// that nothing about the runs has to be known on the host. Without a tile list: seg_off_host [n_seg + 1] gives the run
+// boundaries and every run is a launch of its own. bf16 operands, bf16 or fp32 output.
 extern "C" int llark_gemm_segments(const void* A, long long lda, const void* B, void* C, long long ldc, int c_fp32,
-                                   const int* seg_off_host, int n_seg, const int* seg_tiles_dev, int n_tiles, int N, int K,
-                                   cudaStream_t stream) {
-    if (!A || !B || !C || !seg_off_host || n_seg <= 0 || N <= 0 || K <= 0) return LLARK_EINVAL;
+                                   const int* seg_off_host, int n_seg, const int* seg_tiles_dev, int n_tiles,
+                                   const int* seg_count_dev, int m_total, int N, int K, cudaStream_t stream) {
+    if (!A || !B || !C || n_seg <= 0 || N <= 0 || K <= 0) return LLARK_EINVAL;
     if (seg_tiles_dev && n_tiles > 0 && llark_gemm_get_mode()) {
+        if (m_total <= 0) return LLARK_EINVAL;
         LlarkGemmEpilogue ep;
         ep.kind = LLARK_EPI_SEGMENTS;
         ep.a = seg_tiles_dev;
-        ep.b = nullptr;
+        ep.b = seg_count_dev;
         ep.ld = 0;
         ep.i0 = n_tiles;
         ep.i1 = n_seg;
-        return llark_gemm_ex(A, 0, lda, B, 0, K, C, ldc, c_fp32, nullptr, 0, nullptr, 0, seg_off_host[n_seg], N, K, 0, 0, &ep,
-                             stream);
+        return llark_gemm_ex(A, 0, lda, B, 0, K, C, ldc, c_fp32, nullptr, 0, nullptr, 0, m_total, N, K, 0, 0, &ep, stream);
     }
+    if (!seg_off_host) return LLARK_EINVAL;
     const char* a = static_cast<const char*>(A);
     const char* b = static_cast<const char*>(B);
     char* c = static_cast<char*>(C);

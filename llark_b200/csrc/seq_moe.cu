@@ -1,8 +1,9 @@
 // Routed mixture of experts on the generation path: every token uses `top` of n small gated feed-forwards
 // down(silu(gate x) * (up x)). The router picks experts on the device, one kernel sorts the (token, choice) entries by
 // expert and cuts each expert's run into row tiles, and two grouped GEMM launches walk that tile list (rows gathered
-// through the sort permutation) without a return to the host. Large bf16 steps instead read the segment sizes back once
-// and run every expert's rows through the tcgen05 GEMM core (llark_seq_moe_gather, the GEMMs, llark_seq_silu_mul). The
+// through the sort permutation). Large bf16 steps instead run every expert's rows through the tcgen05 GEMM core in its
+// rows-in-runs mode (llark_seq_moe_gather, llark_gemm_segments with the sort kernel's list of 256-row tiles and its
+// device-side count, llark_seq_silu_mul). Neither route returns to the host. The
 // weighted sum over a token's choices is taken in the order of the choices when the residual is assembled
 // (llark_seq_residual_combine), so a token's result does not depend on what else is in the batch.
 //
@@ -121,7 +122,7 @@ __global__ void route_kernel(const float* __restrict__ logits, long long ld, int
 // One block. meta[0] = number of tiles; tiles[i] = (expert, first sorted row, rows).
 __global__ void sort_kernel(const int* __restrict__ ids, int n_ent, int n_exp, int* __restrict__ perm,
                             int* __restrict__ pos_of, int* __restrict__ tiles, int* __restrict__ meta,
-                            int* __restrict__ seg_off) {
+                            int* __restrict__ seg_off, int* __restrict__ tiles256) {
     extern __shared__ int si[];
     int* cnt = si;               // [n_exp]
     int* off = cnt + n_exp;      // [n_exp + 1]
@@ -130,6 +131,19 @@ __global__ void sort_kernel(const int* __restrict__ ids, int n_ent, int n_exp, i
     __syncthreads();
     for (int i = threadIdx.x; i < n_ent; i += blockDim.x) atomicAdd(&cnt[ids[i]], 1);
     __syncthreads();
+    if (threadIdx.x == 32 && tiles256) {  // the GEMM core's tile list (256-row m-blocks), by another warp
+        int o = 0, nt = 0;
+        for (int e = 0; e < n_exp; ++e) {
+            for (int r = 0; r < cnt[e]; r += 256) {
+                tiles256[3 * nt] = e;
+                tiles256[3 * nt + 1] = o + r;
+                tiles256[3 * nt + 2] = cnt[e] - r < 256 ? cnt[e] - r : 256;
+                ++nt;
+            }
+            o += cnt[e];
+        }
+        meta[1] = nt;
+    }
     if (threadIdx.x == 0) {
         int o = 0, nt = 0;
         for (int e = 0; e < n_exp; ++e) {
@@ -342,11 +356,11 @@ extern "C" int llark_seq_moe_route(const float* logits, long long ld, int* ids, 
 extern "C" int llark_seq_moe_tile_rows(void) { return kTileRows; }
 
 extern "C" int llark_seq_moe_sort(const int* ids, int n_ent, int n_exp, int* perm, int* pos_of, int* tiles, int* meta,
-                                  int* seg_off, cudaStream_t st) {
+                                  int* seg_off, int* tiles256, cudaStream_t st) {
     if (n_ent <= 0 || n_exp <= 0 || !ids || !perm || !pos_of || !tiles || !meta) return LLARK_EINVAL;
     const size_t smem = sizeof(int) * (3 * (size_t)n_exp + 1);
     if (smem > 48 * 1024) return LLARK_EINVAL;
-    sort_kernel<<<1, 1024, smem, st>>>(ids, n_ent, n_exp, perm, pos_of, tiles, meta, seg_off);
+    sort_kernel<<<1, 1024, smem, st>>>(ids, n_ent, n_exp, perm, pos_of, tiles, meta, seg_off, tiles256);
     return check_launch();
 }
 

@@ -761,8 +761,8 @@ def seq_moe_route(logits, n_groups, keep, top, scale):
     return ids, wts
 
 
-# entries (tokens x choices) from which a bf16 step runs every expert's rows through the tcgen05 GEMM core (the segment
-# sizes are then read back once per layer); smaller steps, and fp32, stay on the grouped SIMT kernels without a host read
+# entries (tokens x choices) from which a bf16 step runs every expert's rows through the tcgen05 GEMM core; smaller steps,
+# and fp32, stay on the grouped SIMT kernels. Neither route reads anything back to the host.
 MOE_DENSE_MIN_ENTRIES = 2048
 
 
@@ -774,34 +774,37 @@ def seq_moe_experts(x, ids, w_gate_up, w_down):
     n_exp, ff2, C = w_gate_up.shape
     ff = ff2 // 2
     n_ent = n_tok * top
+    dense = (x.dtype == BF16 and n_ent >= MOE_DENSE_MIN_ENTRIES and C % 8 == 0 and ff % 8 == 0 and C >= 64 and ff >= 64
+             and L.llark_gemm_get_mode() == 1)
     max_tiles = (n_ent + L.llark_seq_moe_tile_rows() - 1) // L.llark_seq_moe_tile_rows() + n_exp
-    ints = torch.empty(2 * n_ent + 3 * max_tiles + 1 + n_exp + 1, device=x.device, dtype=torch.int32)
-    perm, pos_of = ints[:n_ent], ints[n_ent:2 * n_ent]
-    tiles, meta = ints[2 * n_ent:2 * n_ent + 3 * max_tiles], ints[2 * n_ent + 3 * max_tiles:2 * n_ent + 3 * max_tiles + 1]
-    seg_off = ints[2 * n_ent + 3 * max_tiles + 1:]
-    check(L.llark_seq_moe_sort(_p(ids), n_ent, n_exp, _p(perm), _p(pos_of), _p(tiles), _p(meta), _p(seg_off), _stream()),
-          "seq_moe_sort")
+    max256 = (n_ent + 255) // 256 + n_exp if dense else 0
+    ints = torch.empty(2 * n_ent + 3 * max_tiles + 2 + n_exp + 1 + 3 * max256, device=x.device, dtype=torch.int32)
+    o = 0
+
+    def take(n):
+        nonlocal o
+        o += n
+        return ints[o - n:o]
+
+    perm, pos_of, tiles, meta, seg_off, tiles256 = (take(n_ent), take(n_ent), take(3 * max_tiles), take(2),
+                                                    take(n_exp + 1), take(3 * max256))
+    check(L.llark_seq_moe_sort(_p(ids), n_ent, n_exp, _p(perm), _p(pos_of), _p(tiles), _p(meta), _p(seg_off),
+                               _p(tiles256) if dense else None, _stream()), "seq_moe_sort")
     z = torch.empty((n_ent, C), device=x.device, dtype=torch.float32)
-    if x.dtype == BF16 and n_ent >= MOE_DENSE_MIN_ENTRIES and C % 8 == 0 and ff % 8 == 0 and C >= 64 and ff >= 64:
+    act = torch.empty((n_ent, ff), device=x.device, dtype=x.dtype)
+    if dense:
         if not _INITED:
             init()
-        host_off = seg_off.cpu()  # the one host read of the step's routing: rows per expert
-        off_p = ctypes.c_void_p(host_off.data_ptr())
-        off = host_off.tolist()
-        t256 = [v for e in range(n_exp) for r in range(off[e], off[e + 1], 256) for v in (e, r, min(256, off[e + 1] - r))]
-        t256_dev = torch.tensor(t256, dtype=torch.int32).pin_memory().to(x.device, non_blocking=True)
-        n256 = len(t256) // 3
+        count = meta[1:]
         xs = torch.empty((n_ent, C), device=x.device, dtype=x.dtype)
         check(L.llark_seq_moe_gather(_p(x), x.stride(0), _p(perm), top, _p(xs), n_ent, C, 0, _stream()), "seq_moe_gather")
         gu = torch.empty((n_ent, ff2), device=x.device, dtype=x.dtype)
-        act = torch.empty((n_ent, ff), device=x.device, dtype=x.dtype)
-        check(L.llark_gemm_segments(_p(xs), C, _p(w_gate_up), _p(gu), ff2, 0, off_p, n_exp, _p(t256_dev), n256, ff2, C,
-                                    _stream()), "gemm_segments(gate|up)")
+        check(L.llark_gemm_segments(_p(xs), C, _p(w_gate_up), _p(gu), ff2, 0, None, n_exp, _p(tiles256), max256, _p(count),
+                                    n_ent, ff2, C, _stream()), "gemm_segments(gate|up)")
         check(L.llark_seq_silu_mul(_p(gu), _p(act), n_ent, ff, 0, _stream()), "seq_silu_mul")
-        check(L.llark_gemm_segments(_p(act), ff, _p(w_down), _p(z), C, 1, off_p, n_exp, _p(t256_dev), n256, C, ff,
-                                    _stream()), "gemm_segments(down)")
+        check(L.llark_gemm_segments(_p(act), ff, _p(w_down), _p(z), C, 1, None, n_exp, _p(tiles256), max256, _p(count),
+                                    n_ent, C, ff, _stream()), "gemm_segments(down)")
         return z, pos_of
-    act = torch.empty((n_ent, ff), device=x.device, dtype=x.dtype)
     check(L.llark_seq_moe_up(_p(x), x.stride(0), _p(perm), top, _p(w_gate_up), _p(act), _p(tiles), _p(meta), max_tiles,
                              n_ent, ff, C, _actf(x.dtype), _stream()), "seq_moe_up")
     check(L.llark_seq_moe_down(_p(act), _p(w_down), _p(z), _p(tiles), _p(meta), max_tiles, n_ent, C, ff, _actf(x.dtype),
